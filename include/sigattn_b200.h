@@ -1,0 +1,108 @@
+/*
+ * sigattn_b200.h - C ABI of the B200 (sm_100a) sigmoid-attention library.
+ *
+ * O = sigmoid(scale * Q K^T + bias[b] (+ score_mod[b, key])) V on (B, T, H, D) tensors,
+ * with optional causal masking (top-left aligned) and per-batch valid lengths, plus the
+ * recomputation backward producing dQ, dK, dV.
+ *
+ * The reference project (MSDLLCpapers/triton-sigmoid) has no native boundary: its device
+ * code is JIT-compiled from Python.  Each entry point below names the reference routine
+ * whose work it takes over (paths relative to that repository).
+ *
+ * Conventions
+ *  - Every pointer in SigAttnParams is a DEVICE pointer owned by the caller.  The library
+ *    allocates no device memory.  All launches are asynchronous on `stream`.
+ *  - Strides are in ELEMENTS; the head dimension is contiguous (stride 1).  Base pointers
+ *    must be 16-byte aligned and every stride times the element size a multiple of 16 bytes.
+ *  - Return value 0 = launched; negative = rejected before any launch, with a message
+ *    available from sigattn_last_error() on the calling thread.
+ *  - Supported: dtype fp16 / bf16, D in {64, 128}, 1 <= H, B, Tq, Tk (zero-sized problems
+ *    return 0 without launching).
+ */
+#ifndef SIGATTN_B200_H_
+#define SIGATTN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SIGATTN_ABI_VERSION 1
+
+enum SigAttnDtype { SIGATTN_FP16 = 0, SIGATTN_BF16 = 1 };
+
+enum SigAttnFlags {
+  SIGATTN_CAUSAL = 1u << 0, /* key j visible to query i only if j <= i */
+};
+
+enum SigAttnQuery {
+  SIGATTN_Q_ABI_VERSION = 0,
+  SIGATTN_Q_SM_ARCH = 1,        /* 100: the only architecture the kernels are built for */
+  SIGATTN_Q_MAX_HEAD_DIM = 2,   /* 128 */
+  SIGATTN_Q_PARAMS_SIZE = 3     /* sizeof(SigAttnParams), for binding sanity checks */
+};
+
+typedef struct SigAttnParams {
+  uint32_t struct_bytes; /* must be sizeof(SigAttnParams) */
+  int32_t dtype;         /* SigAttnDtype of q, k, v, o, dout, dq, dk, dv */
+  int32_t B, H, D;
+  int32_t Tq, Tk;
+  uint32_t flags;        /* SigAttnFlags */
+  float scale;           /* multiplies Q K^T */
+  float bias_scalar;     /* used for every batch when `bias` is NULL */
+  int32_t device;        /* CUDA device ordinal the pointers live on */
+  int32_t reserved0;
+
+  const void *q, *k, *v; /* (B,Tq,H,D), (B,Tk,H,D), (B,Tk,H,D) */
+  void *o;               /* forward output (B,Tq,H,D); unused by backward */
+  const void *dout;      /* backward only: dO (B,Tq,H,D) */
+  void *dq, *dk, *dv;    /* backward outputs, shaped like q, k, v */
+
+  /* element strides {batch, token, head} */
+  int64_t q_strides[3], k_strides[3], v_strides[3], o_strides[3];
+  int64_t do_strides[3], dq_strides[3], dk_strides[3], dv_strides[3];
+
+  const int32_t *seq_lens_q; /* [B] valid query rows, or NULL = Tq; clamped to [0,Tq] */
+  const int32_t *seq_lens_k; /* [B] valid key rows,   or NULL = Tk; clamped to [0,Tk] */
+  const float *bias;         /* [B] fp32 additive bias, or NULL = bias_scalar */
+  const float *score_mod;    /* [B,Tk] fp32 per-key additive bias (contiguous), or NULL */
+
+  void *workspace;           /* backward: >= sigattn_bwd_workspace_bytes(); forward: unused */
+  size_t workspace_bytes;
+  void *stream;              /* cudaStream_t */
+} SigAttnParams;
+
+/* Forward pass.  Replaces sigmoid_attention_fwd_op + _fwd_dense_kernel
+ * (src/triton_sigmoid/sigmoid_triton_dense.py:23-154, 475-562) and, when seq_lens_* are
+ * given, sigmoid_attn_padded_fwd_op + _fwd_padded_kernel
+ * (src/triton_sigmoid/sigmoid_triton_padded.py:24-171, 517-623).  Rows at or beyond
+ * seq_lens_q[b] are written as zeros. */
+int sigattn_fwd(const SigAttnParams *p);
+
+/* Backward pass (recomputes P; nothing but q, k, v, dO is read).  Replaces
+ * sigmoid_attention_bwd_op + _bwd_dense_dq_kernel + _bwd_dense_dkdv_kernel
+ * (sigmoid_triton_dense.py:162-467, 565-688) and the padded counterparts
+ * (sigmoid_triton_padded.py:179-509, 626-772).  dQ rows >= seq_lens_q[b] and dK/dV rows
+ * >= seq_lens_k[b] are written as zeros.  The fp32 dQ accumulator lives in `workspace`. */
+int sigattn_bwd(const SigAttnParams *p);
+
+/* Bytes of `workspace` sigattn_bwd needs for this problem (fp32 dQ accumulator). */
+size_t sigattn_bwd_workspace_bytes(int32_t B, int32_t Tq, int32_t H, int32_t D);
+
+/* Message for the last failed call made by this host thread ("" if none). */
+const char *sigattn_last_error(void);
+
+/* Static facts about the build; `what` is a SigAttnQuery.  Unknown -> -1. */
+int sigattn_query(int what);
+
+/* Device-side health word of `device`: 0 = no kernel of this library has given up on a
+ * bounded wait since the last call; otherwise a code identifying the wait.  Synchronises
+ * the device.  Negative = CUDA error (see sigattn_last_error). */
+int sigattn_device_status(int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SIGATTN_B200_H_ */

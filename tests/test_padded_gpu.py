@@ -1,0 +1,121 @@
+"""GPU parity of sigmoid_attention_padded with the CPU oracle (public API -> C ABI).
+Follows the reference's tests/test_sigmoid_padded.py: cross-attention shapes, lengths in
+[0.8 T, T], padded rows exactly zero, edge lengths."""
+
+import pytest
+import torch
+
+import triton_sigmoid_b200 as m
+from tests.gpu_util import check_against_oracle, make_inputs, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def _lens(B, T, lo_frac, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(int(lo_frac * T), T + 1, (B,), generator=g, dtype=torch.int32).cuda()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("Tq,Tk", [(128, 128), (256, 512), (512, 256), (1024, 1024)])
+@pytest.mark.parametrize("D", [64, 128])
+def test_parity_sweep(Tq, Tk, D, causal, dtype):
+    if causal and Tq > Tk:
+        pytest.skip("the reference skips causal with more queries than keys")
+    B, H = 3, 2
+    q, k, v, do = make_inputs(B, Tq, Tk, H, D, dtype, std=0.5, seed=Tq + Tk + D, requires_grad=True)
+    lq, lk = _lens(B, Tq, 0.8, 1), _lens(B, Tk, 0.8, 2)
+    check_against_oracle(m.sigmoid_attention_padded, q, k, v, do, dtype, lens_q=lq, lens_k=lk, is_causal=causal)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_benchmark_varlen_config_reduced(causal):
+    """bf16, N_max=2048, H=8, D=64, lengths uniform in [256, 2048] with N(0,1) garbage in the
+    padding (benchmark configuration 3, with 4 of its 16 sequences to keep the oracle quick)."""
+    B, T, H, D = 4, 2048, 8, 64
+    q, k, v, do = make_inputs(B, T, T, H, D, torch.bfloat16, seed=2, requires_grad=True)
+    lens = torch.randint(256, 2049, (16,), generator=torch.Generator().manual_seed(2), dtype=torch.int32)[:B].cuda()
+    check_against_oracle(m.sigmoid_attention_padded, q, k, v, do, torch.bfloat16, lens_q=lens, lens_k=lens,
+                         is_causal=causal)
+
+
+@pytest.mark.parametrize("lens", [[16, 64], [128, 256], [1, 255], [129, 0]])
+def test_edge_lengths(lens):
+    q, k, v, do = make_inputs(2, 256, 256, 2, 64, torch.float16, std=0.5, seed=sum(lens), requires_grad=True)
+    l = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    check_against_oracle(m.sigmoid_attention_padded, q, k, v, do, torch.float16, lens_q=l, lens_k=l)
+
+
+def test_zero_length_keys_give_zeros_without_nan():
+    q, k, v, do = make_inputs(2, 128, 128, 2, 64, torch.float16, seed=3, requires_grad=True)
+    lk = torch.tensor([0, 100], dtype=torch.int32, device="cuda")
+    out = m.sigmoid_attention_padded(q, k, v, seq_lens_k=lk)
+    out.backward(do)
+    for t in (out, q.grad, k.grad, v.grad):
+        assert torch.isfinite(t).all()
+    assert out[0].abs().max().item() == 0 and q.grad[0].abs().max().item() == 0
+
+
+def test_none_lengths_mean_no_padding_and_match_dense():
+    q, k, v, _ = make_inputs(2, 384, 384, 2, 64, torch.float16, std=0.5, seed=4)
+    a = m.sigmoid_attention_padded(q, k, v)
+    full = torch.full((2,), 384, dtype=torch.int32, device="cuda")
+    b = m.sigmoid_attention_padded(q, k, v, seq_lens_k=full, seq_lens_q=full)
+    c = m.sigmoid_attention(q, k, v)
+    assert torch.equal(a, b)
+    assert (a.float() - c.float()).abs().max().item() <= 2e-3
+
+
+def test_int64_lengths_are_cast():
+    q, k, v, _ = make_inputs(2, 128, 128, 2, 64, torch.float16, seed=5)
+    l32 = torch.tensor([100, 60], dtype=torch.int32, device="cuda")
+    assert torch.equal(m.sigmoid_attention_padded(q, k, v, seq_lens_k=l32, seq_lens_q=l32),
+                       m.sigmoid_attention_padded(q, k, v, seq_lens_k=l32.long(), seq_lens_q=l32.long()))
+
+
+def test_out_of_range_lengths_are_clamped():
+    q, k, v, _ = make_inputs(2, 128, 128, 2, 64, torch.float16, seed=6)
+    big = torch.tensor([500, -3], dtype=torch.int32, device="cuda")
+    out = m.sigmoid_attention_padded(q, k, v, seq_lens_k=big, seq_lens_q=big, sigmoid_bias=-1.0)
+    assert out.shape == q.shape and torch.isfinite(out).all()
+    assert out[1].abs().max().item() == 0
+
+
+def test_score_mod_cross_attention():
+    q, k, v, do = make_inputs(2, 192, 320, 2, 64, torch.bfloat16, std=0.5, seed=7, requires_grad=True)
+    sm = torch.randn(2, 320, device="cuda")
+    lq = torch.tensor([192, 50], dtype=torch.int32, device="cuda")
+    lk = torch.tensor([300, 320], dtype=torch.int32, device="cuda")
+    check_against_oracle(m.sigmoid_attention_padded, q, k, v, do, torch.bfloat16, lens_q=lq, lens_k=lk, score_mod=sm)
+
+
+def test_causality_with_padding():
+    q, k, v, _ = make_inputs(2, 512, 512, 2, 64, torch.float16, seed=8)
+    l = torch.tensor([512, 400], dtype=torch.int32, device="cuda")
+    o1 = m.sigmoid_attention_padded(q, k, v, seq_lens_k=l, seq_lens_q=l, is_causal=True)
+    k2 = k.clone()
+    k2[:, 260:] += 3.0
+    o2 = m.sigmoid_attention_padded(q, k2, v, seq_lens_k=l, seq_lens_q=l, is_causal=True)
+    assert torch.equal(o1[:, :260], o2[:, :260])
+
+
+def test_nan_in_padding_does_not_leak():
+    """Padded key/value/query rows may hold anything, NaN included."""
+    q, k, v, do = make_inputs(2, 256, 256, 2, 64, torch.float16, std=0.5, seed=9, requires_grad=True)
+    l = torch.tensor([200, 77], dtype=torch.int32, device="cuda")
+    with torch.no_grad():
+        for t in (q, k, v, do):
+            t[0, 200:] = float("nan")
+            t[1, 77:] = float("nan")
+    out = m.sigmoid_attention_padded(q, k, v, seq_lens_k=l, seq_lens_q=l)
+    out.backward(do)
+    for t in (out, q.grad, k.grad, v.grad):
+        assert torch.isfinite(t).all()
+
+
+def test_forward_is_deterministic():
+    q, k, v, _ = make_inputs(3, 640, 640, 2, 128, torch.bfloat16, seed=10)
+    l = _lens(3, 640, 0.3, 3)
+    a = m.sigmoid_attention_padded(q, k, v, seq_lens_k=l, seq_lens_q=l, is_causal=True)
+    assert torch.equal(a, m.sigmoid_attention_padded(q, k, v, seq_lens_k=l, seq_lens_q=l, is_causal=True))

@@ -1,0 +1,302 @@
+// Host side of the C ABI declared in include/sigattn_b200.h: argument checks, TMA tensor
+// maps, kernel selection and launches.  No device memory is allocated here.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/sigattn_b200.h"
+#include "bwd_kernel.cuh"
+#include "fwd_kernel.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define SIG_CUDA(expr)                                                                            \
+  do {                                                                                            \
+    cudaError_t e_ = (expr);                                                                      \
+    if (e_ != cudaSuccess) return fail(-100, "%s failed: %s", #expr, cudaGetErrorString(e_));     \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Tensor map over a (B, T, H, D) tensor with element strides {sb, st, sh} and unit stride in
+// D.  TMA dimensions are ordered (d, h, t, b); one box is 64 elements of d by `box_rows`
+// tokens of one head of one batch, written to shared memory with the 128-byte swizzle.
+// Rows at or beyond T read as zeros.
+int make_map(CUtensorMap* m, const void* base, int dtype, int B, int T, int H, int D, const int64_t* strides,
+             int box_rows, const char* name) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(-101, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return fail(-3, "%s: base pointer must be 16-byte aligned", name);
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] <= 0 || (strides[i] * 2) % 16 != 0)
+      return fail(-3, "%s: stride %d (%lld elements) must be positive and a multiple of 8 elements", name, i,
+                  (long long)strides[i]);
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+  cuuint64_t gstr[3] = {(cuuint64_t)strides[2] * 2, (cuuint64_t)strides[1] * 2, (cuuint64_t)strides[0] * 2};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, dtype == SIGATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   const_cast<void*>(base), dims, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-102, "%s: cuTensorMapEncodeTiled failed with CUresult %d", name, (int)r);
+  return 0;
+}
+
+int check_common(const SigAttnParams* p, bool backward) {
+  if (!p) return fail(-1, "params is NULL");
+  if (p->struct_bytes != sizeof(SigAttnParams))
+    return fail(-1, "struct_bytes %u != sizeof(SigAttnParams) %zu (ABI mismatch)", p->struct_bytes,
+                sizeof(SigAttnParams));
+  if (p->dtype != SIGATTN_FP16 && p->dtype != SIGATTN_BF16) return fail(-2, "unsupported dtype %d (fp16=0, bf16=1)", p->dtype);
+  if (p->D != 64 && p->D != 128) return fail(-2, "unsupported head dimension %d (64 or 128)", p->D);
+  if (p->B < 0 || p->H < 0 || p->Tq < 0 || p->Tk < 0) return fail(-2, "negative extent");
+  if (p->H > 65535 || p->B > 65535) return fail(-2, "B and H must not exceed 65535");
+  if (p->B == 0 || p->H == 0) return 1;  // nothing to do
+  if (!p->q || !p->k || !p->v) return fail(-1, "q, k, v must not be NULL");
+  if (!backward && !p->o) return fail(-1, "o must not be NULL");
+  if (backward && (!p->dout || !p->dq || !p->dk || !p->dv)) return fail(-1, "dout, dq, dk, dv must not be NULL");
+  return 0;
+}
+
+bool is_contiguous(const int64_t* s, int T, int H, int D) {
+  return s[2] == D && s[1] == (int64_t)H * D && s[0] == (int64_t)T * H * D;
+}
+
+// Zero-fill a (B,T,H,D) 16-bit tensor; only used for degenerate problems (no keys / no queries).
+int zero_fill(void* ptr, const int64_t* strides, int B, int T, int H, int D, cudaStream_t stream, const char* name) {
+  if (T == 0) return 0;
+  if (!is_contiguous(strides, T, H, D)) return fail(-2, "%s: an empty problem needs a contiguous output", name);
+  SIG_CUDA(cudaMemsetAsync(ptr, 0, (size_t)B * T * H * D * 2, stream));
+  return 0;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t enter(int dev) {
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return e;
+    // Always set the device: on a host thread that has made no runtime call yet (an autograd
+    // worker, say) this is what binds the primary context, which the driver-level tensor-map
+    // encoder needs.
+    e = cudaSetDevice(dev);
+    switched = (e == cudaSuccess) && prev != dev;
+    return e;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+  SIG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return 0;
+}
+
+template <int D, bool kBF16, bool kScoreMod>
+int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm) {
+  using namespace sigattn;
+  auto kernel = sigattn_fwd_kernel<D, kBF16, kScoreMod>;
+  constexpr int smem = FwdSmem<D>::kDynBytes;
+  if (int rc = set_smem(kernel, smem)) return rc;
+  FwdParams fp;
+  fp.o = p->o;
+  fp.o_sb = p->o_strides[0];
+  fp.o_st = p->o_strides[1];
+  fp.o_sh = p->o_strides[2];
+  fp.lens_q = p->seq_lens_q;
+  fp.lens_k = p->seq_lens_k;
+  fp.bias = p->bias;
+  fp.score_mod = p->score_mod;
+  fp.scale = p->scale;
+  fp.bias_scalar = p->bias_scalar;
+  fp.B = p->B;
+  fp.H = p->H;
+  fp.Tq = p->Tq;
+  fp.Tk = p->Tk;
+  fp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
+  fp.n_qblk = (p->Tq + kFwdBlockM - 1) / kFwdBlockM;
+  dim3 grid(fp.n_qblk, p->H, p->B);
+  kernel<<<grid, kFwdThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(qm, km, vm, fp);
+  SIG_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <int D, bool kBF16>
+int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
+               const CUtensorMap& dom) {
+  using namespace sigattn;
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  const size_t need = sigattn_bwd_workspace_bytes(p->B, p->Tq, p->H, p->D);
+  if (p->workspace_bytes < need || (need && !p->workspace))
+    return fail(-4, "backward workspace too small: %zu bytes given, %zu needed", p->workspace_bytes, need);
+  if ((reinterpret_cast<uintptr_t>(p->workspace) & 15u) != 0) return fail(-3, "workspace must be 16-byte aligned");
+  float* dq_acc = static_cast<float*>(p->workspace);
+  SIG_CUDA(cudaMemsetAsync(dq_acc, 0, need, stream));
+
+  BwdParams bp;
+  bp.dq_acc = dq_acc;
+  bp.dk = p->dk;
+  bp.dv = p->dv;
+  bp.dk_sb = p->dk_strides[0]; bp.dk_st = p->dk_strides[1]; bp.dk_sh = p->dk_strides[2];
+  bp.dv_sb = p->dv_strides[0]; bp.dv_st = p->dv_strides[1]; bp.dv_sh = p->dv_strides[2];
+  bp.lens_q = p->seq_lens_q;
+  bp.lens_k = p->seq_lens_k;
+  bp.bias = p->bias;
+  bp.score_mod = p->score_mod;
+  bp.scale = p->scale;
+  bp.bias_scalar = p->bias_scalar;
+  bp.B = p->B; bp.H = p->H; bp.Tq = p->Tq; bp.Tk = p->Tk;
+  bp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
+  bp.n_kvblk = (p->Tk + kBwdTileKV - 1) / kBwdTileKV;
+
+  {
+    auto kernel = sigattn_bwd_kernel<D, kBF16>;
+    constexpr int smem = BwdSmem<D>::kDynBytes;
+    if (int rc = set_smem(kernel, smem)) return rc;
+    dim3 grid(bp.n_kvblk, p->H, p->B);
+    kernel<<<grid, kBwdThreads, smem, stream>>>(qm, km, vm, dom, bp);
+    SIG_CUDA(cudaGetLastError());
+  }
+  {
+    // dQ = scale * accumulator, rounded to the 16-bit type
+    DqConvertParams cp;
+    cp.acc = dq_acc;
+    cp.dq = p->dq;
+    cp.sb = p->dq_strides[0]; cp.st = p->dq_strides[1]; cp.sh = p->dq_strides[2];
+    cp.B = p->B; cp.T = p->Tq; cp.H = p->H;
+    cp.scale = p->scale;
+    const long long chunks = (long long)p->B * p->Tq * p->H * (D / 8);
+    const int threads = 256;
+    const long long blocks_ll = (chunks + threads - 1) / threads;
+    const int blocks = (int)(blocks_ll > 148LL * 64 ? 148LL * 64 : blocks_ll);
+    sigattn_dq_convert_kernel<D, kBF16><<<blocks, threads, 0, stream>>>(cp);
+    SIG_CUDA(cudaGetLastError());
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* sigattn_last_error(void) { return g_err; }
+
+int sigattn_query(int what) {
+  switch (what) {
+    case SIGATTN_Q_ABI_VERSION: return SIGATTN_ABI_VERSION;
+    case SIGATTN_Q_SM_ARCH: return 100;
+    case SIGATTN_Q_MAX_HEAD_DIM: return 128;
+    case SIGATTN_Q_PARAMS_SIZE: return (int)sizeof(SigAttnParams);
+    default: return -1;
+  }
+}
+
+size_t sigattn_bwd_workspace_bytes(int32_t B, int32_t Tq, int32_t H, int32_t D) {
+  if (B <= 0 || Tq <= 0 || H <= 0 || D <= 0) return 0;
+  return (size_t)B * (size_t)Tq * (size_t)H * (size_t)D * sizeof(float);
+}
+
+int sigattn_device_status(int device) {
+  DeviceGuard g;
+  SIG_CUDA(g.enter(device));
+  SIG_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  SIG_CUDA(cudaMemcpyFromSymbol(&v, sigattn::g_status_word, sizeof(int)));
+  if (v != 0) {
+    int zero = 0;
+    SIG_CUDA(cudaMemcpyToSymbol(sigattn::g_status_word, &zero, sizeof(int)));
+  }
+  return v;
+}
+
+int sigattn_fwd(const SigAttnParams* p) {
+  g_err[0] = 0;
+  int rc = check_common(p, false);
+  if (rc < 0) return rc;
+  if (rc == 1) return 0;
+  DeviceGuard g;
+  SIG_CUDA(g.enter(p->device));
+  if (p->Tq == 0) return 0;
+  if (p->Tk == 0)  // no keys at all: the output is all zeros
+    return zero_fill(p->o, p->o_strides, p->B, p->Tq, p->H, p->D, static_cast<cudaStream_t>(p->stream), "o");
+  CUtensorMap qm, km, vm;
+  if ((rc = make_map(&qm, p->q, p->dtype, p->B, p->Tq, p->H, p->D, p->q_strides, 128, "q"))) return rc;
+  if ((rc = make_map(&km, p->k, p->dtype, p->B, p->Tk, p->H, p->D, p->k_strides, 128, "k"))) return rc;
+  if ((rc = make_map(&vm, p->v, p->dtype, p->B, p->Tk, p->H, p->D, p->v_strides, 128, "v"))) return rc;
+  if ((reinterpret_cast<uintptr_t>(p->o) & 15u) != 0) return fail(-3, "o: base pointer must be 16-byte aligned");
+  for (int i = 0; i < 3; ++i)
+    if (p->o_strides[i] % 8 != 0) return fail(-3, "o: strides must be multiples of 8 elements");
+
+  const bool bf = p->dtype == SIGATTN_BF16;
+  const bool sm = p->score_mod != nullptr;
+#define SIG_FWD(DD, BF, SM) return launch_fwd<DD, BF, SM>(p, qm, km, vm)
+  if (p->D == 64) {
+    if (bf) { if (sm) SIG_FWD(64, true, true); else SIG_FWD(64, true, false); }
+    else    { if (sm) SIG_FWD(64, false, true); else SIG_FWD(64, false, false); }
+  } else {
+    if (bf) { if (sm) SIG_FWD(128, true, true); else SIG_FWD(128, true, false); }
+    else    { if (sm) SIG_FWD(128, false, true); else SIG_FWD(128, false, false); }
+  }
+#undef SIG_FWD
+  return fail(-2, "unreachable");
+}
+
+int sigattn_bwd(const SigAttnParams* p) {
+  g_err[0] = 0;
+  int rc = check_common(p, true);
+  if (rc < 0) return rc;
+  if (rc == 1) return 0;
+  DeviceGuard g;
+  SIG_CUDA(g.enter(p->device));
+  if (p->Tq == 0 || p->Tk == 0) {
+    // no query or no key: every gradient is zero
+    cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+    if ((rc = zero_fill(p->dq, p->dq_strides, p->B, p->Tq, p->H, p->D, stream, "dq"))) return rc;
+    if ((rc = zero_fill(p->dk, p->dk_strides, p->B, p->Tk, p->H, p->D, stream, "dk"))) return rc;
+    return zero_fill(p->dv, p->dv_strides, p->B, p->Tk, p->H, p->D, stream, "dv");
+  }
+  CUtensorMap qm, km, vm, dom;
+  if ((rc = make_map(&qm, p->q, p->dtype, p->B, p->Tq, p->H, p->D, p->q_strides, 128, "q"))) return rc;
+  if ((rc = make_map(&km, p->k, p->dtype, p->B, p->Tk, p->H, p->D, p->k_strides, 128, "k"))) return rc;
+  if ((rc = make_map(&vm, p->v, p->dtype, p->B, p->Tk, p->H, p->D, p->v_strides, 128, "v"))) return rc;
+  if ((rc = make_map(&dom, p->dout, p->dtype, p->B, p->Tq, p->H, p->D, p->do_strides, 128, "dout"))) return rc;
+  const void* outs[3] = {p->dq, p->dk, p->dv};
+  const int64_t* ostr[3] = {p->dq_strides, p->dk_strides, p->dv_strides};
+  for (int t = 0; t < 3; ++t) {
+    if ((reinterpret_cast<uintptr_t>(outs[t]) & 15u) != 0) return fail(-3, "gradient pointers must be 16-byte aligned");
+    for (int i = 0; i < 3; ++i)
+      if (ostr[t][i] % 8 != 0) return fail(-3, "gradient strides must be multiples of 8 elements");
+  }
+  if (p->D == 64) return p->dtype == SIGATTN_BF16 ? launch_bwd<64, true>(p, qm, km, vm, dom) : launch_bwd<64, false>(p, qm, km, vm, dom);
+  return p->dtype == SIGATTN_BF16 ? launch_bwd<128, true>(p, qm, km, vm, dom) : launch_bwd<128, false>(p, qm, km, vm, dom);
+}
+
+}  // extern "C"

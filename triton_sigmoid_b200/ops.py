@@ -1,0 +1,369 @@
+"""torch.library custom ops around the C ABI, and the public functions.
+
+Mirrors the reference's operator layer: four ops (dense / padded, forward / backward) with
+``register_fake`` and ``register_autograd`` so eager autograd and ``torch.compile`` both work
+(reference: ``src/triton_sigmoid/sigmoid_triton_dense.py:475-753`` and
+``src/triton_sigmoid/sigmoid_triton_padded.py:517-846``), and the two public wrappers with
+the reference's signatures, defaults, validation and error texts
+(``sigmoid_triton_dense.py:761-853``, ``sigmoid_triton_padded.py:853-1010``).
+
+All arithmetic happens in the CUDA library; nothing here computes attention.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import _cabi
+
+_NS = "sigattn_b200"
+_SUPPORTED_DTYPES = (torch.float16, torch.bfloat16)
+_DEVICE_OK: dict = {}
+
+
+def _require_b200(dev: torch.device) -> None:
+    """The kernels exist for sm_100 only; anything else is an error, never a fallback."""
+    if dev.type != "cuda":
+        raise RuntimeError(f"triton_sigmoid_b200 runs on CUDA tensors only, got device '{dev}'")
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    ok = _DEVICE_OK.get(idx)
+    if ok is None:
+        major, minor = torch.cuda.get_device_capability(idx)
+        ok = _DEVICE_OK[idx] = major == 10
+        if not ok:
+            _DEVICE_OK[idx] = False
+    if not _DEVICE_OK[idx]:
+        major, minor = torch.cuda.get_device_capability(idx)
+        raise RuntimeError(f"triton_sigmoid_b200 requires an sm_100 GPU (B200), found sm_{major}{minor}")
+
+
+def _strides3(t: torch.Tensor):
+    sb, st, sh, sd = t.stride()
+    assert sd == 1
+    return (ctypes.c_int64 * 3)(sb, st, sh)
+
+
+def _base_params(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal) -> _cabi.SigAttnParams:
+    B, Tq, H, D = q.shape
+    p = _cabi.SigAttnParams()
+    p.struct_bytes = ctypes.sizeof(_cabi.SigAttnParams)
+    p.dtype = _cabi.SIGATTN_BF16 if q.dtype == torch.bfloat16 else _cabi.SIGATTN_FP16
+    p.B, p.H, p.D, p.Tq, p.Tk = B, H, D, Tq, k.shape[1]
+    p.flags = _cabi.SIGATTN_CAUSAL if is_causal else 0
+    p.scale = float(scale)
+    p.bias_scalar = 0.0
+    p.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    p.q_strides, p.k_strides, p.v_strides = _strides3(q), _strides3(k), _strides3(v)
+    p.seq_lens_q = seq_lens_q.data_ptr() if seq_lens_q is not None else None
+    p.seq_lens_k = seq_lens_k.data_ptr() if seq_lens_k is not None else None
+    p.bias = bias.data_ptr()
+    p.score_mod = score_mod.data_ptr() if score_mod is not None else None
+    p.stream = torch.cuda.current_stream(q.device).cuda_stream
+    return p
+
+
+def _prep_aux(q, bias, score_mod, seq_lens_q, seq_lens_k):
+    bias = bias.to(device=q.device, dtype=torch.float32).contiguous()
+    if score_mod is not None:
+        score_mod = score_mod.to(device=q.device, dtype=torch.float32).contiguous()
+    if seq_lens_q is not None:
+        seq_lens_q = seq_lens_q.to(device=q.device, dtype=torch.int32).contiguous()
+    if seq_lens_k is not None:
+        seq_lens_k = seq_lens_k.to(device=q.device, dtype=torch.int32).contiguous()
+    return bias, score_mod, seq_lens_q, seq_lens_k
+
+
+def _check_kernel_inputs(q, k, v):
+    _require_b200(q.device)
+    if q.dtype not in _SUPPORTED_DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError(
+            f"triton_sigmoid_b200 kernels take float16 or bfloat16 q/k/v of one dtype, got "
+            f"{q.dtype}, {k.dtype}, {v.dtype}"
+        )
+    if q.shape[-1] not in (64, 128):
+        raise NotImplementedError(f"kernel head dimension must be 64 or 128, got {q.shape[-1]}")
+
+
+def _run_fwd(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal) -> torch.Tensor:
+    _check_kernel_inputs(q, k, v)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    out = torch.empty_like(q)
+    if out.numel() == 0:
+        return out
+    bias, score_mod, seq_lens_q, seq_lens_k = _prep_aux(q, bias, score_mod, seq_lens_q, seq_lens_k)
+    p = _base_params(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal)
+    p.o = out.data_ptr()
+    p.o_strides = _strides3(out)
+    _cabi.check(_cabi.load().sigattn_fwd(ctypes.byref(p)), "sigattn_fwd")
+    return out
+
+
+def _run_bwd(q, k, v, do, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal):
+    _check_kernel_inputs(q, k, v)
+    q, k, v, do = q.contiguous(), k.contiguous(), v.contiguous(), do.contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if q.numel() == 0 and k.numel() == 0:
+        return dq, dk, dv
+    bias, score_mod, seq_lens_q, seq_lens_k = _prep_aux(q, bias, score_mod, seq_lens_q, seq_lens_k)
+    lib = _cabi.load()
+    B, Tq, H, D = q.shape
+    ws_bytes = lib.sigattn_bwd_workspace_bytes(B, Tq, H, D)
+    ws = torch.empty(max(ws_bytes, 16) // 4, dtype=torch.float32, device=q.device)
+    p = _base_params(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal)
+    p.dout = do.data_ptr()
+    p.do_strides = _strides3(do)
+    p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    p.dq_strides, p.dk_strides, p.dv_strides = _strides3(dq), _strides3(dk), _strides3(dv)
+    p.workspace = ws.data_ptr()
+    p.workspace_bytes = ws.numel() * 4
+    _cabi.check(lib.sigattn_bwd(ctypes.byref(p)), "sigattn_bwd")
+    return dq, dk, dv
+
+
+# ----------------------------------------------------------------------------- dense ops
+@torch.library.custom_op(f"{_NS}::sigmoid_attention_fwd", mutates_args=())
+def sigmoid_attention_fwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, bias: torch.Tensor,
+                             score_mod: Optional[torch.Tensor], sm_scale: float, is_causal: bool) -> torch.Tensor:
+    return _run_fwd(Q, K, V, bias, score_mod, None, None, sm_scale, is_causal)
+
+
+@sigmoid_attention_fwd_op.register_fake
+def _(Q, K, V, bias, score_mod, sm_scale, is_causal):
+    return torch.empty_like(Q, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op(f"{_NS}::sigmoid_attention_bwd", mutates_args=())
+def sigmoid_attention_bwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, dO: torch.Tensor,
+                             bias: torch.Tensor, score_mod: Optional[torch.Tensor], sm_scale: float,
+                             is_causal: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _run_bwd(Q, K, V, dO, bias, score_mod, None, None, sm_scale, is_causal)
+
+
+@sigmoid_attention_bwd_op.register_fake
+def _(Q, K, V, dO, bias, score_mod, sm_scale, is_causal):
+    c = torch.contiguous_format
+    return (torch.empty_like(Q, memory_format=c), torch.empty_like(K, memory_format=c),
+            torch.empty_like(V, memory_format=c))
+
+
+def _dense_setup_context(ctx, inputs, output):
+    Q, K, V, bias, score_mod, sm_scale, is_causal = inputs
+    ctx.save_for_backward(Q, K, V, bias, score_mod)
+    ctx.sm_scale = sm_scale
+    ctx.is_causal = is_causal
+
+
+def _dense_backward(ctx, dO):
+    Q, K, V, bias, score_mod = ctx.saved_tensors
+    dQ, dK, dV = sigmoid_attention_bwd_op(Q, K, V, dO, bias, score_mod, ctx.sm_scale, ctx.is_causal)
+    return dQ, dK, dV, None, None, None, None
+
+
+sigmoid_attention_fwd_op.register_autograd(_dense_backward, setup_context=_dense_setup_context)
+
+
+# ----------------------------------------------------------------------------- padded ops
+@torch.library.custom_op(f"{_NS}::sigmoid_attn_padded_fwd", mutates_args=())
+def sigmoid_attn_padded_fwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, seq_lens_k: torch.Tensor,
+                               seq_lens_q: torch.Tensor, bias: torch.Tensor, score_mod: Optional[torch.Tensor],
+                               sm_scale: float, is_causal: bool) -> torch.Tensor:
+    return _run_fwd(Q, K, V, bias, score_mod, seq_lens_q, seq_lens_k, sm_scale, is_causal)
+
+
+@sigmoid_attn_padded_fwd_op.register_fake
+def _(Q, K, V, seq_lens_k, seq_lens_q, bias, score_mod, sm_scale, is_causal):
+    return torch.empty_like(Q, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op(f"{_NS}::sigmoid_attn_padded_bwd", mutates_args=())
+def sigmoid_attn_padded_bwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, dO: torch.Tensor,
+                               seq_lens_k: torch.Tensor, seq_lens_q: torch.Tensor, bias: torch.Tensor,
+                               score_mod: Optional[torch.Tensor], sm_scale: float,
+                               is_causal: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _run_bwd(Q, K, V, dO, bias, score_mod, seq_lens_q, seq_lens_k, sm_scale, is_causal)
+
+
+@sigmoid_attn_padded_bwd_op.register_fake
+def _(Q, K, V, dO, seq_lens_k, seq_lens_q, bias, score_mod, sm_scale, is_causal):
+    c = torch.contiguous_format
+    return (torch.empty_like(Q, memory_format=c), torch.empty_like(K, memory_format=c),
+            torch.empty_like(V, memory_format=c))
+
+
+def _padded_setup_context(ctx, inputs, output):
+    Q, K, V, seq_lens_k, seq_lens_q, bias, score_mod, sm_scale, is_causal = inputs
+    ctx.save_for_backward(Q, K, V, seq_lens_k, seq_lens_q, bias, score_mod)
+    ctx.sm_scale = sm_scale
+    ctx.is_causal = is_causal
+
+
+def _padded_backward(ctx, dO):
+    Q, K, V, seq_lens_k, seq_lens_q, bias, score_mod = ctx.saved_tensors
+    dQ, dK, dV = sigmoid_attn_padded_bwd_op(Q, K, V, dO, seq_lens_k, seq_lens_q, bias, score_mod, ctx.sm_scale,
+                                            ctx.is_causal)
+    return dQ, dK, dV, None, None, None, None, None, None
+
+
+sigmoid_attn_padded_fwd_op.register_autograd(_padded_backward, setup_context=_padded_setup_context)
+
+
+# ----------------------------------------------------------------------------- public API
+def _validate_qkv(query, key, value):
+    if query.dim() != 4 or key.dim() != 4 or value.dim() != 4:
+        raise ValueError("Expected query, key, and value to be 4D tensors")
+    B, T_q, H, D = query.shape
+    B_k, T_k, H_k, D_k = key.shape
+    B_v, T_v, H_v, D_v = value.shape
+    if B != B_k or B != B_v:
+        raise ValueError(f"Batch size mismatch: Q={B}, K={B_k}, V={B_v}")
+    if H != H_k or H != H_v:
+        raise ValueError(f"Number of heads mismatch: Q={H}, K={H_k}, V={H_v}")
+    if D != D_k or D != D_v:
+        raise ValueError(f"Head dimension mismatch: Q={D}, K={D_k}, V={D_v}")
+    return B, T_q, T_k, T_v, H, D
+
+
+def _kernel_head_dim(D: int) -> int:
+    if D <= 64:
+        return 64
+    if D <= 128:
+        return 128
+    raise NotImplementedError(f"head dimension {D} is larger than the 128 the kernels support")
+
+
+def _pad_head_dim(x: torch.Tensor, D_kernel: int) -> torch.Tensor:
+    """Zero-extend the head dimension (zeros add nothing to Q.K and only yield extra output
+    columns, which the caller slices away again)."""
+    D = x.shape[-1]
+    return x if D == D_kernel else F.pad(x, (0, D_kernel - D))
+
+
+def _check_dtype(query, key, value):
+    if query.dtype == torch.float32:
+        raise NotImplementedError(
+            "float32 inputs are not supported by the sm_100a kernels (16-bit tensor-core inputs only); "
+            "cast to float16 or bfloat16"
+        )
+    if query.dtype not in _SUPPORTED_DTYPES:
+        raise NotImplementedError(f"unsupported dtype {query.dtype}: use float16 or bfloat16")
+    if key.dtype != query.dtype or value.dtype != query.dtype:
+        raise ValueError(f"query, key and value must share one dtype, got {query.dtype}, {key.dtype}, {value.dtype}")
+
+
+def sigmoid_attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    is_causal: bool = False,
+    scale: Optional[float] = None,
+    sigmoid_bias: Optional[float] = None,
+    score_mod: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Sigmoid attention for dense (same-length) sequences, differentiable in q, k, v.
+
+    ``output = sigmoid(Q @ K^T * scale + sigmoid_bias + score_mod[key]) @ V`` on
+    ``[B, T, H, D]`` tensors.  ``scale`` defaults to ``1/sqrt(D)``, ``sigmoid_bias`` to
+    ``-log(T)``; ``score_mod`` is an optional ``[B, T]`` additive per-key bias without
+    gradient.  Same contract as the reference's ``sigmoid_attention``
+    (``sigmoid_triton_dense.py:761-853``).
+    """
+    B, T_q, T_k, T_v, H, D = _validate_qkv(query, key, value)
+    if T_q != T_k or T_q != T_v:
+        raise ValueError(f"Dense attention requires same sequence length for Q, K, V, got {T_q}, {T_k}, {T_v}")
+    if score_mod is not None:
+        if score_mod.shape != (B, T_k):
+            raise ValueError(f"score_mod must have shape ({B}, {T_k}), got {score_mod.shape}")
+        score_mod = score_mod.contiguous()
+    _check_dtype(query, key, value)
+
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    Dk = _kernel_head_dim(D)
+    query, key, value = (_pad_head_dim(t, Dk).contiguous() for t in (query, key, value))
+
+    if torch.compiler.is_compiling():
+        for x in (query, key, value):
+            torch._dynamo.mark_static(x, -2)  # heads
+            torch._dynamo.mark_static(x, -1)  # head dimension
+
+    if sigmoid_bias is None:
+        bias = torch.full((B,), -math.log(float(T_q)) if T_q > 0 else 0.0, dtype=torch.float32, device=query.device)
+    else:
+        bias = torch.full((B,), float(sigmoid_bias), dtype=torch.float32, device=query.device)
+
+    out = sigmoid_attention_fwd_op(query, key, value, bias, score_mod, float(scale), bool(is_causal))
+    return out if Dk == D else out[..., :D]
+
+
+def sigmoid_attention_padded(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    seq_lens_k: Optional[torch.Tensor] = None,
+    seq_lens_q: Optional[torch.Tensor] = None,
+    is_causal: bool = False,
+    scale: Optional[float] = None,
+    sigmoid_bias: Optional[float] = None,
+    score_mod: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Sigmoid attention for sequences with trailing padding, differentiable in q, k, v.
+
+    ``query`` is ``[B, T_q, H, D]``, ``key`` / ``value`` are ``[B, T_k, H, D]``;
+    ``seq_lens_k`` / ``seq_lens_q`` (``[B]``, integer) give the number of valid tokens per
+    batch element (``None`` = all).  Output rows at or beyond ``seq_lens_q[b]`` are zero, and
+    so are the matching gradient rows.  ``sigmoid_bias`` defaults to ``-log(seq_lens_k[b])``.
+    Same contract as the reference's ``sigmoid_attention_padded``
+    (``sigmoid_triton_padded.py:853-1010``); lengths outside ``[0, T]`` are clamped.
+    """
+    B, T_q, T_k, T_v, H, D = _validate_qkv(query, key, value)
+    if T_k != T_v:
+        raise ValueError(f"Key and value sequence lengths must match, got K={T_k}, V={T_v}")
+
+    if seq_lens_k is None:
+        seq_lens_k = torch.full((B,), T_k, dtype=torch.int32, device=query.device)
+    else:
+        if seq_lens_k.shape != (B,):
+            raise ValueError(f"seq_lens_k must have shape ({B},), got {seq_lens_k.shape}")
+        if seq_lens_k.dtype != torch.int32:
+            seq_lens_k = seq_lens_k.to(torch.int32)
+        seq_lens_k = seq_lens_k.to(query.device).contiguous()
+    if seq_lens_q is None:
+        seq_lens_q = torch.full((B,), T_q, dtype=torch.int32, device=query.device)
+    else:
+        if seq_lens_q.shape != (B,):
+            raise ValueError(f"seq_lens_q must have shape ({B},), got {seq_lens_q.shape}")
+        if seq_lens_q.dtype != torch.int32:
+            seq_lens_q = seq_lens_q.to(torch.int32)
+        seq_lens_q = seq_lens_q.to(query.device).contiguous()
+
+    if score_mod is not None:
+        if score_mod.shape != (B, T_k):
+            raise ValueError(f"score_mod must have shape ({B}, {T_k}), got {score_mod.shape}")
+        score_mod = score_mod.contiguous()
+    _check_dtype(query, key, value)
+
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    Dk = _kernel_head_dim(D)
+    query, key, value = (_pad_head_dim(t, Dk).contiguous() for t in (query, key, value))
+
+    if torch.compiler.is_compiling():
+        for x in (query, key, value):
+            torch._dynamo.mark_static(x, -2)  # heads
+            torch._dynamo.mark_static(x, -1)  # head dimension
+
+    if sigmoid_bias is None:
+        # -log(0) = +inf for an empty key set; every probability is masked there anyway
+        bias = -torch.log(seq_lens_k.clamp(min=0, max=T_k).float())
+    else:
+        bias = torch.full((B,), float(sigmoid_bias), dtype=torch.float32, device=query.device)
+
+    out = sigmoid_attn_padded_fwd_op(query, key, value, seq_lens_k, seq_lens_q, bias, score_mod, float(scale),
+                                     bool(is_causal))
+    return out if Dk == D else out[..., :D]
