@@ -72,6 +72,12 @@ typedef struct SigAttnParams {
   void *workspace;           /* backward: >= sigattn_bwd_workspace_bytes(); forward: unused */
   size_t workspace_bytes;
   void *stream;              /* cudaStream_t */
+
+  /* Optional cudaEvent_t pair (NULL = off), recorded on `stream` immediately before and after
+   * the launch of the main attention kernel of the call, so that a caller can time that
+   * kernel alone (the backward call also zero-fills and converts the dQ accumulator). */
+  void *ev_main_start;
+  void *ev_main_stop;
 } SigAttnParams;
 
 /* Forward pass.  Replaces sigmoid_attention_fwd_op + _fwd_dense_kernel

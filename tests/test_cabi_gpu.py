@@ -1,0 +1,84 @@
+"""Calls the C ABI directly with raw device pointers (no torch ops in between) and checks the
+results, the error reporting on a GPU box, and the event hooks."""
+
+import ctypes
+import math
+
+import pytest
+import torch
+
+from oracle import sigattn_oracle as orc
+from triton_sigmoid_b200 import _cabi
+from triton_sigmoid_b200.profiling import time_main_kernel
+
+pytestmark = pytest.mark.gpu
+
+
+def _s3(t):
+    return (ctypes.c_int64 * 3)(*t.stride()[:3])
+
+
+def test_raw_forward_and_backward_calls():
+    lib = _cabi.load()
+    torch.manual_seed(1)
+    B, T, H, D = 2, 200, 3, 128
+    q, k, v, do = [torch.randn(B, T, H, D, device="cuda", dtype=torch.float16) * 0.5 for _ in range(4)]
+    o, dq, dk, dv = [torch.full_like(q, float("nan")) for _ in range(4)]
+    ws = torch.empty(lib.sigattn_bwd_workspace_bytes(B, T, H, D) // 4, dtype=torch.float32, device="cuda")
+    p = _cabi.SigAttnParams()
+    p.struct_bytes = ctypes.sizeof(p)
+    p.dtype, p.B, p.H, p.D, p.Tq, p.Tk = _cabi.SIGATTN_FP16, B, H, D, T, T
+    p.flags = _cabi.SIGATTN_CAUSAL
+    p.scale = 1.0 / math.sqrt(D)
+    p.bias_scalar = -math.log(T)  # bias pointer left NULL: scalar bias for every batch
+    p.device = 0
+    p.q, p.k, p.v, p.o, p.dout = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr()
+    p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    for name in ("q", "k", "v", "o", "do", "dq", "dk", "dv"):
+        setattr(p, name + "_strides", _s3(q))
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * 4
+    p.stream = torch.cuda.current_stream().cuda_stream
+    assert lib.sigattn_fwd(ctypes.byref(p)) == 0, lib.sigattn_last_error()
+    assert lib.sigattn_bwd(ctypes.byref(p)) == 0, lib.sigattn_last_error()
+    assert lib.sigattn_device_status(0) == 0
+    ref_o = orc.sigattn_forward(q, k, v, is_causal=True)
+    ref = orc.sigattn_backward(q, k, v, do, is_causal=True)
+    assert (o.float().cpu() - ref_o).abs().max().item() <= 2e-3
+    for g, r in zip((dq, dk, dv), ref):
+        assert ((g.float().cpu() - r).norm() / r.norm()).item() <= 1e-2
+
+
+def test_workspace_too_small_is_reported():
+    lib = _cabi.load()
+    q = torch.zeros(1, 128, 1, 64, device="cuda", dtype=torch.float16)
+    p = _cabi.SigAttnParams()
+    p.struct_bytes = ctypes.sizeof(p)
+    p.dtype, p.B, p.H, p.D, p.Tq, p.Tk = 0, 1, 1, 64, 128, 128
+    p.scale = 0.125
+    p.q = p.k = p.v = p.dout = p.dq = p.dk = p.dv = q.data_ptr()
+    for name in ("q", "k", "v", "do", "dq", "dk", "dv"):
+        setattr(p, name + "_strides", _s3(q))
+    p.workspace, p.workspace_bytes = q.data_ptr(), 64
+    assert lib.sigattn_bwd(ctypes.byref(p)) < 0
+    assert b"workspace too small" in lib.sigattn_last_error()
+
+
+def test_misaligned_pointer_is_reported():
+    lib = _cabi.load()
+    q = torch.zeros(1, 128, 1, 64 + 8, device="cuda", dtype=torch.float16)
+    p = _cabi.SigAttnParams()
+    p.struct_bytes = ctypes.sizeof(p)
+    p.dtype, p.B, p.H, p.D, p.Tq, p.Tk = 0, 1, 1, 64, 128, 128
+    p.q = q.data_ptr() + 2
+    p.k = p.v = p.o = q.data_ptr()
+    for name in ("q", "k", "v", "o"):
+        setattr(p, name + "_strides", _s3(q))
+    assert lib.sigattn_fwd(ctypes.byref(p)) < 0
+    assert b"16-byte aligned" in lib.sigattn_last_error()
+
+
+def test_event_hooks_time_the_main_kernel():
+    q, k, v, do = [torch.randn(2, 1024, 4, 64, device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+    for direction in ("fwd", "bwd"):
+        ms = time_main_kernel(direction, q, k, v, do, iters=3)
+        assert len(ms) == 3 and all(0 < x < 100 for x in ms)

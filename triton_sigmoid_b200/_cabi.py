@@ -67,6 +67,8 @@ class SigAttnParams(ctypes.Structure):
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
         ("stream", ctypes.c_void_p),
+        ("ev_main_start", ctypes.c_void_p),
+        ("ev_main_stop", ctypes.c_void_p),
     ]
 
 

@@ -352,19 +352,26 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull), t & 1, abort_flag, kSiteBase + 12));
       if (!ok) break;
       tc_fence_after_sync();
+      uint32_t rbuf[2][32];
+      tmem_ld32(s_addr, rbuf[0]);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32_sync(s_addr + c * 32, r);
+        uint32_t(&r)[32] = rbuf[c];
+        tmem_ld_wait_for(r);
+        if (c == 0) tmem_ld32(s_addr + 32, rbuf[1]);
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float pe = sigmoid_from_log2(fmaf(__uint_as_float(r[i]), c1, c0));
+        for (int i = 0; i < 16; ++i) {
+          const float2 t = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])),
+                                      make_float2(c1, c1), make_float2(c0, c0));
+          float2 pe = sigmoid2_from_log2<kBF16>(t);
           if (need_mask) {
-            const int q = qc0 + c * 32 + i;
-            pe = (row_ok && q >= q_lo && q < Lq) ? pe : 0.0f;
+            const int q = qc0 + c * 32 + 2 * i;
+            pe.x = (row_ok && q >= q_lo && q < Lq) ? pe.x : 0.0f;
+            pe.y = (row_ok && q + 1 >= q_lo && q + 1 < Lq) ? pe.y : 0.0f;
           }
-          pv[c * 32 + i] = pe;
+          pv[c * 32 + 2 * i] = pe.x;
+          pv[c * 32 + 2 * i + 1] = pe.y;
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) pk[i] = pack2<kBF16>(pv[c * 32 + 2 * i], pv[c * 32 + 2 * i + 1]);
@@ -382,21 +389,24 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         if (!ok) break;
       }
       tc_fence_after_sync();
+      tmem_ld32(dp_addr, rbuf[0]);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32_sync(dp_addr + c * 32, r);
+        uint32_t(&r)[32] = rbuf[c];
+        tmem_ld_wait_for(r);
+        if (c == 0) tmem_ld32(dp_addr + 32, rbuf[1]);
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = pv[c * 32 + 2 * i], p1 = pv[c * 32 + 2 * i + 1];
-          float d0 = p0 * (1.0f - p0) * __uint_as_float(r[2 * i]);
-          float d1 = p1 * (1.0f - p1) * __uint_as_float(r[2 * i + 1]);
+          const float2 pp = make_float2(pv[c * 32 + 2 * i], pv[c * 32 + 2 * i + 1]);
+          // dS = P (1 - P) dP = (P - P^2) dP
+          const float2 w = __ffma2_rn(make_float2(-pp.x, -pp.y), pp, pp);
+          float2 d = __fmul2_rn(w, make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
           if (need_mask) {
-            d0 = (p0 != 0.0f) ? d0 : 0.0f;  // masked elements have P exactly 0; keeps NaN/Inf padding out
-            d1 = (p1 != 0.0f) ? d1 : 0.0f;
+            d.x = (pp.x != 0.0f) ? d.x : 0.0f;  // masked elements have P exactly 0; keeps NaN/Inf padding out
+            d.y = (pp.y != 0.0f) ? d.y : 0.0f;
           }
-          pk[i] = pack2<kBF16>(d0, d1);
+          pk[i] = pack2<kBF16>(d.x, d.y);
         }
         tmem_st16(dp_addr + c * 16, pk);
         // shared-memory copy for the dQ GEMM: row = key, 64 query columns per 128-byte swizzled line

@@ -69,12 +69,40 @@ struct FwdSmem {
 };
 
 // sigmoid(x) with x given in the base-2 domain (t = x * log2(e)).
-// e = 2^-|t| in (0,1]; sigmoid = (t < 0 ? e : 1) / (1 + e).  Relative accuracy is kept for
-// strongly negative logits (the default bias is -log(T)), unlike 0.5 + 0.5 tanh(x/2).
-__device__ __forceinline__ float sigmoid_from_log2(float t) {
-  const float e = ex2_approx(-fabsf(t));
-  const float r = rcp_approx(1.0f + e);
-  return (t < 0.0f ? e : 1.0f) * r;
+// e = 2^-|t| in (0,1] (one MUFU op); sigmoid = (t < 0 ? e : 1) / (1 + e).  This keeps RELATIVE
+// accuracy for strongly negative logits (the default bias is -log(T), so a typical probability
+// is ~1/T), which 0.5 + 0.5 tanh(x/2) does not.  1/(1+e) on [0,1] is a minimax polynomial on
+// the FMA pipe instead of a second MUFU op: the MUFU unit (16 results / clock / SM) is what
+// bounds this kernel.  Maximum relative error of the polynomial: 5.1e-5 (degree 5, used for
+// fp16, whose own rounding is 4.9e-4) and 3.0e-4 (degree 4, used for bf16, rounding 3.9e-3).
+template <bool kBF16>
+__device__ __forceinline__ float2 rcp1p_poly(float2 e) {
+  float2 r;
+  if constexpr (kBF16) {
+    r = make_float2(0.1522425264120102f, 0.1522425264120102f);
+    r = __ffma2_rn(r, e, make_float2(-0.5328524708747864f, -0.5328524708747864f));
+    r = __ffma2_rn(r, e, make_float2(0.8658902645111084f, 0.8658902645111084f));
+    r = __ffma2_rn(r, e, make_float2(-0.9848342537879944f, -0.9848342537879944f));
+    r = __ffma2_rn(r, e, make_float2(0.9997026324272156f, 0.9997026324272156f));
+  } else {
+    r = make_float2(-0.1044827550649643f, -0.1044827550649643f);
+    r = __ffma2_rn(r, e, make_float2(0.41793352365493774f, 0.41793352365493774f));
+    r = __ffma2_rn(r, e, make_float2(-0.7705690264701843f, -0.7705690264701843f));
+    r = __ffma2_rn(r, e, make_float2(0.9534193277359009f, 0.9534193277359009f));
+    r = __ffma2_rn(r, e, make_float2(-0.9962754845619202f, -0.9962754845619202f));
+    r = __ffma2_rn(r, e, make_float2(0.9999489784240723f, 0.9999489784240723f));
+  }
+  return r;
+}
+
+// Two sigmoids at once; t holds the logits times log2(e).
+template <bool kBF16>
+__device__ __forceinline__ float2 sigmoid2_from_log2(float2 t) {
+  float2 e = make_float2(ex2_approx(-fabsf(t.x)), ex2_approx(-fabsf(t.y)));
+  const float2 r = rcp1p_poly<kBF16>(e);
+  e.x = t.x < 0.0f ? e.x : 1.0f;
+  e.y = t.y < 0.0f ? e.y : 1.0f;
+  return __fmul2_rn(e, r);
 }
 
 template <int D, bool kBF16, bool kScoreMod>
@@ -315,27 +343,30 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       int lim = Lk - 1;
       if (p.causal) lim = min(lim, row);
       const bool need_mask = (col0 + kTileN > Lk) || (p.causal && col0 + kTileN - 1 > q0 + 128 * s);
-#pragma unroll 1
+      // two register buffers: the load of chunk c+1 is in flight while chunk c is computed
+      uint32_t rbuf[2][32];
+      tmem_ld32(s_addr, rbuf[0]);
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32_sync(s_addr + c * 32, r);
+        uint32_t(&r)[32] = rbuf[c & 1];
+        tmem_ld_wait_for(r);
+        if (c + 1 < 4) tmem_ld32(s_addr + (c + 1) * 32, rbuf[(c + 1) & 1]);
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float t0 = fmaf(__uint_as_float(r[2 * i]), c1, c0);
-          float t1 = fmaf(__uint_as_float(r[2 * i + 1]), c1, c0);
+          float2 t = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])),
+                                make_float2(c1, c1), make_float2(c0, c0));
           const int col = col0 + c * 32 + 2 * i;
           if constexpr (kScoreMod) {
-            t0 = fmaf(col < p.Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t0);
-            t1 = fmaf(col + 1 < p.Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t1);
+            t.x = fmaf(col < p.Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t.x);
+            t.y = fmaf(col + 1 < p.Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t.y);
           }
-          float p0 = sigmoid_from_log2(t0);
-          float p1 = sigmoid_from_log2(t1);
+          float2 pr = sigmoid2_from_log2<kBF16>(t);
           if (need_mask) {
-            p0 = (col <= lim) ? p0 : 0.0f;
-            p1 = (col + 1 <= lim) ? p1 : 0.0f;
+            pr.x = (col <= lim) ? pr.x : 0.0f;
+            pr.y = (col + 1 <= lim) ? pr.y : 0.0f;
           }
-          pk[i] = pack2<kBF16>(p0, p1);
+          pk[i] = pack2<kBF16>(pr.x, pr.y);
         }
         tmem_st16(s_addr + c * 16, pk);
       }

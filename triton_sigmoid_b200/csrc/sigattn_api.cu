@@ -144,8 +144,11 @@ int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   fp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
   fp.n_qblk = (p->Tq + kFwdBlockM - 1) / kFwdBlockM;
   dim3 grid(fp.n_qblk, p->H, p->B);
-  kernel<<<grid, kFwdThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(qm, km, vm, fp);
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  if (p->ev_main_start) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream));
+  kernel<<<grid, kFwdThreads, smem, stream>>>(qm, km, vm, fp);
   SIG_CUDA(cudaGetLastError());
+  if (p->ev_main_stop) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_stop), stream));
   return 0;
 }
 
@@ -182,8 +185,10 @@ int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
     constexpr int smem = BwdSmem<D>::kDynBytes;
     if (int rc = set_smem(kernel, smem)) return rc;
     dim3 grid(bp.n_kvblk, p->H, p->B);
+    if (p->ev_main_start) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream));
     kernel<<<grid, kBwdThreads, smem, stream>>>(qm, km, vm, dom, bp);
     SIG_CUDA(cudaGetLastError());
+    if (p->ev_main_stop) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_stop), stream));
   }
   {
     // dQ = scale * accumulator, rounded to the 16-bit type
