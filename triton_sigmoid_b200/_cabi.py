@@ -84,12 +84,13 @@ def load() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        if not os.path.exists(LIB_PATH):
+        path = os.environ.get("SIGATTN_B200_LIB", LIB_PATH)  # explicit override of the library location
+        if not os.path.exists(path):
             raise ImportError(
-                f"{LIB_PATH} is missing: build it with `python -m triton_sigmoid_b200.build` "
+                f"{path} is missing: build it with `python -m triton_sigmoid_b200.build` "
                 "(needs nvcc with sm_100a support). This package has no other execution path."
             )
-        lib = ctypes.CDLL(LIB_PATH)
+        lib = ctypes.CDLL(path)
         lib.sigattn_fwd.argtypes = [ctypes.POINTER(SigAttnParams)]
         lib.sigattn_fwd.restype = ctypes.c_int
         lib.sigattn_bwd.argtypes = [ctypes.POINTER(SigAttnParams)]

@@ -46,20 +46,22 @@ def find_nvcc() -> str:
     raise RuntimeError("nvcc not found: set NVCC or put it on PATH")
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, out: str = None, extra_flags=()) -> str:
+    """Compile the library.  `out` / `extra_flags` build a variant elsewhere (experiments)."""
+    target = out or LIB_PATH
+    if out is None and not force and not needs_build():
         return LIB_PATH
-    os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [find_nvcc(), *NVCC_FLAGS]
+    os.makedirs(os.path.dirname(target), exist_ok=True)
+    cmd = [find_nvcc(), *NVCC_FLAGS, *extra_flags]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", LIB_PATH, os.path.join(CSRC, "sigattn_api.cu")]
+    cmd += ["-o", target, os.path.join(CSRC, "sigattn_api.cu")]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed building " + LIB_PATH)
-    return LIB_PATH
+        raise RuntimeError("nvcc failed building " + target)
+    return target
 
 
 if __name__ == "__main__":

@@ -23,8 +23,8 @@
 // dQ = scale * accumulator is rounded to the 16-bit type by sigattn_dq_convert_kernel.
 #pragma once
 
-#include "fwd_kernel.cuh"
 #include "ptx.cuh"
+#include "sigmoid_math.cuh"
 
 namespace sigattn {
 
@@ -238,93 +238,105 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     }
   } else if (warp == 13) {
     // ============================================================ tcgen05 issuer
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_st = make_idesc(128, 128, kBF16, false, false);  // S^T, dP^T
       constexpr uint32_t idesc_acc = make_idesc(128, D, kBF16, false, true);    // dV, dK: A in TMEM, B rows = contraction
       constexpr uint32_t idesc_dq = make_idesc(128, D, kBF16, true, true);      // dQ: both operands row = contraction
       const uint32_t k_s = smem_base + L::kKOff;
       const uint32_t v_s = smem_base + L::kVOff;
       const uint32_t ds_s = smem_base + L::kDsOff;
+      // descriptor bases; per-MMA descriptors differ only in the start-address field (>> 4)
+      const uint64_t k_km = smem_desc_sw128(k_s, 16, 1024);        // K_j, rows = M
+      const uint64_t v_km = smem_desc_sw128(v_s, 16, 1024);        // V_j, rows = M
+      const uint64_t k_mn = smem_desc_sw128(k_s, 16384, 1024);     // K_j, rows = contraction
+      const uint64_t ds_mn = smem_desc_sw128(ds_s, 16384, 1024);   // dS^T, rows = contraction
+      const uint64_t q_km0 = smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
+      const uint64_t do_km0 = smem_desc_sw128(smem_base + L::kDoOff, 16, 1024);
+      const uint64_t q_mn0 = smem_desc_sw128(smem_base + L::kQOff, 16384, 1024);
+      const uint64_t do_mn0 = smem_desc_sw128(smem_base + L::kDoOff, 16384, 1024);
+      constexpr uint64_t kStageStep = (uint64_t)(kTileBytes >> 4);
       // C[key, query] = A[key, :] . B[query, :] over the head dimension
-      auto issue_kmajor = [&](uint32_t dcol, uint32_t a_s, uint32_t b_s) {
+      auto issue_kmajor = [&](uint32_t dcol, uint64_t a_d, uint64_t b_d) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tmem + dcol, smem_desc_sw128(a_s + off, 16, 1024), smem_desc_sw128(b_s + off, 16, 1024), idesc_st, kk > 0);
+          const uint64_t off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          mma_ss(leader, tmem + dcol, a_d + off, b_d + off, idesc_st, kk > 0);
         }
       };
       // acc[key, d] += A^T[key, query] (TMEM, 16-bit) . B[query, d] (smem tile of query rows)
-      auto issue_acc = [&](uint32_t dcol, uint32_t acol, uint32_t b_s, bool first) {
+      auto issue_acc = [&](uint32_t dcol, uint32_t acol, uint64_t b_d, bool first) {
+        const uint32_t acc0 = first ? 0u : 1u;
 #pragma unroll
         for (int kk = 0; kk < kBwdTileQ / 16; ++kk) {
-          mma_ts(tmem + dcol, tmem + acol + 64 * (kk >> 2) + 8 * (kk & 3), smem_desc_sw128(b_s + kk * 2048, 16384, 1024),
-                 idesc_acc, (!first || kk > 0) ? 1u : 0u);
+          mma_ts(leader, tmem + dcol, tmem + acol + 64 * (kk >> 2) + 8 * (kk & 3), b_d + (uint64_t)(kk * (2048 >> 4)), idesc_acc,
+                 kk > 0 ? 1u : acc0);
         }
       };
       auto ragged_q = [&](int t) { return (i_begin + t) * kBwdTileQ + kBwdTileQ > Lq; };
-      bool ok = mbar_wait(bar(L::kKvFull), 0, abort_flag, kSiteBase + 3);
-      if (kv0 + kBwdTileKV > Lk) ok = ok && mbar_wait(bar(L::kKvFix), 0, abort_flag, kSiteBase + 20);
-      ok = ok && mbar_wait(bar(L::kQFull + 0), 0, abort_flag, kSiteBase + 4);
-      if (ragged_q(0)) ok = ok && mbar_wait(bar(L::kQdoFix), 0, abort_flag, kSiteBase + 21);
+      bool ok = mbar_wait_warp(bar(L::kKvFull), 0, abort_flag, kSiteBase + 3);
+      if (kv0 + kBwdTileKV > Lk) ok = ok && mbar_wait_warp(bar(L::kKvFix), 0, abort_flag, kSiteBase + 20);
+      ok = ok && mbar_wait_warp(bar(L::kQFull + 0), 0, abort_flag, kSiteBase + 4);
+      if (ragged_q(0)) ok = ok && mbar_wait_warp(bar(L::kQdoFix), 0, abort_flag, kSiteBase + 21);
       if (ok) {
-        issue_kmajor(kColS, k_s, smem_base + L::kQOff);
-        mma_commit(bar(L::kSFull));
+        issue_kmajor(kColS, k_km, q_km0);
+        mma_commit(leader, bar(L::kSFull));
       }
-      ok = ok && mbar_wait(bar(L::kDoFull + 0), 0, abort_flag, kSiteBase + 5);
+      ok = ok && mbar_wait_warp(bar(L::kDoFull + 0), 0, abort_flag, kSiteBase + 5);
       if (ok) {
-        issue_kmajor(kColDp, v_s, smem_base + L::kDoOff);
-        mma_commit(bar(L::kDpFull));
+        issue_kmajor(kColDp, v_km, do_km0);
+        mma_commit(leader, bar(L::kDpFull));
       }
       for (int t = 0; t < n_q && ok; ++t) {
         const int st = t & 1;
-        const uint32_t q_s = smem_base + L::kQOff + st * kTileBytes;
-        const uint32_t do_s = smem_base + L::kDoOff + st * kTileBytes;
+        const uint64_t q_mn = q_mn0 + st * kStageStep;
+        const uint64_t do_mn = do_mn0 + st * kStageStep;
         const int st_n = st ^ 1;
         const uint32_t ph_n = ((t + 1) >> 1) & 1;
         // dV += P^T dO
-        ok = mbar_wait(bar(L::kPReady), t & 1, abort_flag, kSiteBase + 6);
+        ok = mbar_wait_warp(bar(L::kPReady), t & 1, abort_flag, kSiteBase + 6);
         if (!ok) break;
         tc_fence_after_sync();
-        issue_acc(kColDv, kColS, do_s, t == 0);
+        issue_acc(kColDv, kColS, do_mn, t == 0);
         // S^T of the next tile may overwrite P^T now
         if (t + 1 < n_q) {
-          ok = mbar_wait(bar(L::kQFull + st_n), ph_n, abort_flag, kSiteBase + 7);
-          if (ragged_q(t + 1)) ok = ok && mbar_wait(bar(L::kQdoFix), 0, abort_flag, kSiteBase + 22);
+          ok = mbar_wait_warp(bar(L::kQFull + st_n), ph_n, abort_flag, kSiteBase + 7);
+          if (ragged_q(t + 1)) ok = ok && mbar_wait_warp(bar(L::kQdoFix), 0, abort_flag, kSiteBase + 22);
           if (!ok) break;
-          issue_kmajor(kColS, k_s, smem_base + L::kQOff + st_n * kTileBytes);
-          mma_commit(bar(L::kSFull));
+          issue_kmajor(kColS, k_km, q_km0 + st_n * kStageStep);
+          mma_commit(leader, bar(L::kSFull));
         }
         // dK += dS^T Q
-        ok = mbar_wait(bar(L::kDsReady), t & 1, abort_flag, kSiteBase + 8);
+        ok = mbar_wait_warp(bar(L::kDsReady), t & 1, abort_flag, kSiteBase + 8);
         if (!ok) break;
         tc_fence_after_sync();
-        issue_acc(kColDk, kColDp, q_s, t == 0);
+        issue_acc(kColDk, kColDp, q_mn, t == 0);
         // dQ_i = dS K (needs the previous dQ tile drained out of TMEM)
-        ok = mbar_wait(bar(L::kDqEmpty), (t & 1) ^ 1, abort_flag, kSiteBase + 9);
+        ok = mbar_wait_warp(bar(L::kDqEmpty), (t & 1) ^ 1, abort_flag, kSiteBase + 9);
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
-          mma_ss(tmem + kColDq, smem_desc_sw128(ds_s + kk * 2048, 16384, 1024),
-                 smem_desc_sw128(k_s + kk * 2048, 16384, 1024), idesc_dq, kk > 0);
+          mma_ss(leader, tmem + kColDq, ds_mn + (uint64_t)(kk * (2048 >> 4)), k_mn + (uint64_t)(kk * (2048 >> 4)), idesc_dq,
+                 kk > 0);
         }
-        mma_commit(bar(L::kDqFull));
-        mma_commit(bar(L::kQEmpty + st));
-        mma_commit(bar(L::kDoEmpty + st));
+        mma_commit(leader, bar(L::kDqFull));
+        mma_commit(leader, bar(L::kQEmpty + st));
+        mma_commit(leader, bar(L::kDoEmpty + st));
         if (t + 1 < n_q) {
           if (kDqAliased) {
             // dQ_i sits in the dP^T columns: wait until it has been drained
-            ok = mbar_wait(bar(L::kDqEmpty), t & 1, abort_flag, kSiteBase + 10);
+            ok = mbar_wait_warp(bar(L::kDqEmpty), t & 1, abort_flag, kSiteBase + 10);
             if (!ok) break;
             tc_fence_after_sync();
           }
-          ok = mbar_wait(bar(L::kDoFull + st_n), ph_n, abort_flag, kSiteBase + 11);
+          ok = mbar_wait_warp(bar(L::kDoFull + st_n), ph_n, abort_flag, kSiteBase + 11);
           if (!ok) break;
-          issue_kmajor(kColDp, v_s, smem_base + L::kDoOff + st_n * kTileBytes);
-          mma_commit(bar(L::kDpFull));
+          issue_kmajor(kColDp, v_km, do_km0 + st_n * kStageStep);
+          mma_commit(leader, bar(L::kDpFull));
         }
       }
-      if (ok) mma_commit(bar(L::kDkvFull));
+      if (ok) mma_commit(leader, bar(L::kDkvFull));
     }
   } else if (warp < 8) {
     // ============================================================ compute groups

@@ -5,23 +5,25 @@
 // (src/triton_sigmoid/sigmoid_triton_dense.py:23-154) and _fwd_padded_kernel
 // (src/triton_sigmoid/sigmoid_triton_padded.py:24-171).
 //
-// Structure (sm_100a):
-//   warps 0-3   sigmoid group 0: owns query rows [q0, q0+128)      (one thread per row)
-//   warps 4-7   sigmoid group 1: owns query rows [q0+128, q0+256)
-//   warp  8     TMA producer: Q tiles once, then K_j / V_j through a ring of smem stages
-//   warp  9     tcgen05 issuer: S_s = Q_s K_j^T (smem x smem -> TMEM fp32) and
-//               O_s += P_s V_j (TMEM x smem -> TMEM fp32); also owns the TMEM allocation
-//   warps 10-11 idle (pad the CTA to three warpgroups)
+// Structure (sm_100a, 18 warps):
+//   warps 0-7    sigmoid groups of query tile 0 (rows [q0, q0+128)): warps 0-3 take key columns
+//                [0,64) of every score tile, warps 4-7 columns [64,128); one thread per row
+//   warps 8-15   the same for query tile 1 (rows [q0+128, q0+256))
+//   warp  16     TMA producer: Q tiles once, then K_j / V_j through a ring of smem stages
+//   warp  17     tcgen05 issuer: S = Q_s K_j^T (smem x smem -> TMEM fp32) and
+//                O_s += P V_j (TMEM x smem -> TMEM fp32); also owns the TMEM allocation
 // There is no row normaliser in sigmoid attention, so O simply accumulates in TMEM over the
-// whole key loop; the sigmoid groups turn S into 16-bit P in place (P aliases the first 64
-// columns of S) and signal the issuer.  The two query tiles ping-pong so that tensor-core
-// work for one overlaps the sigmoid of the other.
+// whole key loop.  The (query tile, key tile) jobs are processed in a fixed order through a
+// small ring of S buffers in TMEM (3 when D = 64, 2 when D = 128): the issuer computes the
+// scores of a later job while the sigmoid groups turn earlier ones into 16-bit P in place
+// (each group writes P over the start of the columns it has just read) and signal the issuer.
 //
 // Masking: key tiles beyond the causal diagonal or the valid key length are skipped
 // entirely; tiles that straddle either boundary apply an element predicate.
 #pragma once
 
 #include "ptx.cuh"
+#include "sigmoid_math.cuh"
 
 namespace sigattn {
 
@@ -39,14 +41,29 @@ struct FwdParams {
   int n_qblk;  // ceil(Tq / 256)
 };
 
-constexpr int kFwdThreads = 384;
+#ifdef SIG_TRACE
+// experiment-only cycle counters of block (0,0,0): [role][counter]
+__device__ long long g_trace[64];
+#define SIG_T0() const long long t0_ = clock64()
+#define SIG_TACC(var) var += clock64() - t0_
+#else
+#define SIG_T0()
+#define SIG_TACC(var)
+#endif
+#ifndef SIG_FWD_CHUNK
+#define SIG_FWD_CHUNK 32
+#endif
+constexpr int kFwdSigmoidWarps = 16;
+constexpr int kFwdProducerWarp = 16;
+constexpr int kFwdIssuerWarp = 17;
+constexpr int kFwdThreads = 18 * 32;
 constexpr int kFwdBlockM = 256;  // query rows per CTA (two 128-row tiles)
 constexpr int kTileN = 128;      // key rows per step
-constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
 struct FwdSmem {
   static constexpr int kStages = (D == 64) ? 4 : 2;
+  static constexpr int kSBufs = (D == 64) ? 3 : 2;  // S buffers in TMEM
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQOff + 2 * kTileBytes;
@@ -58,9 +75,9 @@ struct FwdSmem {
   static constexpr int kKEmpty = kKFull + kStages;    // [kStages]
   static constexpr int kVFull = kKEmpty + kStages;    // [kStages]
   static constexpr int kVEmpty = kVFull + kStages;    // [kStages]
-  static constexpr int kSFull = kVEmpty + kStages;    // [2]
-  static constexpr int kPFull = kSFull + 2;           // [2]
-  static constexpr int kOFull = kPFull + 2;           // [1]
+  static constexpr int kSFull = kVEmpty + kStages;    // [kSBufs]
+  static constexpr int kPFull = kSFull + kSBufs;      // [kSBufs]
+  static constexpr int kOFull = kPFull + kSBufs;      // [1]
   static constexpr int kVFix = kOFull + 1;            // [1] padded rows of the last V tile zeroed
   static constexpr int kNumBars = kVFix + 1;
   static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int)
@@ -68,41 +85,41 @@ struct FwdSmem {
   static constexpr int kDynBytes = kTotal + 1024;  // slack to align the base to 1024 bytes
 };
 
-// sigmoid(x) with x given in the base-2 domain (t = x * log2(e)).
-// e = 2^-|t| in (0,1] (one MUFU op); sigmoid = (t < 0 ? e : 1) / (1 + e).  This keeps RELATIVE
-// accuracy for strongly negative logits (the default bias is -log(T), so a typical probability
-// is ~1/T), which 0.5 + 0.5 tanh(x/2) does not.  1/(1+e) on [0,1] is a minimax polynomial on
-// the FMA pipe instead of a second MUFU op: the MUFU unit (16 results / clock / SM) is what
-// bounds this kernel.  Maximum relative error of the polynomial: 5.1e-5 (degree 5, used for
-// fp16, whose own rounding is 4.9e-4) and 3.0e-4 (degree 4, used for bf16, rounding 3.9e-3).
-template <bool kBF16>
-__device__ __forceinline__ float2 rcp1p_poly(float2 e) {
-  float2 r;
-  if constexpr (kBF16) {
-    r = make_float2(0.1522425264120102f, 0.1522425264120102f);
-    r = __ffma2_rn(r, e, make_float2(-0.5328524708747864f, -0.5328524708747864f));
-    r = __ffma2_rn(r, e, make_float2(0.8658902645111084f, 0.8658902645111084f));
-    r = __ffma2_rn(r, e, make_float2(-0.9848342537879944f, -0.9848342537879944f));
-    r = __ffma2_rn(r, e, make_float2(0.9997026324272156f, 0.9997026324272156f));
-  } else {
-    r = make_float2(-0.1044827550649643f, -0.1044827550649643f);
-    r = __ffma2_rn(r, e, make_float2(0.41793352365493774f, 0.41793352365493774f));
-    r = __ffma2_rn(r, e, make_float2(-0.7705690264701843f, -0.7705690264701843f));
-    r = __ffma2_rn(r, e, make_float2(0.9534193277359009f, 0.9534193277359009f));
-    r = __ffma2_rn(r, e, make_float2(-0.9962754845619202f, -0.9962754845619202f));
-    r = __ffma2_rn(r, e, make_float2(0.9999489784240723f, 0.9999489784240723f));
+// Turns 64 score columns of one TMEM lane (this thread's query row) into 16-bit probabilities,
+// written back over the first 32 of those columns.  col0 = key index of the first column,
+// lim = largest visible key index of this row (used only when kMask).
+template <bool kBF16, bool kScoreMod, bool kMask>
+__device__ __forceinline__ void fwd_sigmoid_half_tile(uint32_t s_addr, float c1, float c0, int col0, int lim,
+                                                      const float* sm_row, int Tk) {
+  // two register buffers: the load of the next chunk is in flight while one is computed
+  constexpr int kCh = SIG_FWD_CHUNK;  // score columns per chunk
+  constexpr int kNCh = 64 / kCh;
+  uint32_t rbuf[2][kCh];
+  tmem_ld(s_addr, rbuf[0]);
+#pragma unroll
+  for (int c = 0; c < kNCh; ++c) {
+    uint32_t(&r)[kCh] = rbuf[c & 1];
+    tmem_ld_wait_for(r);
+    if (c + 1 < kNCh) tmem_ld(s_addr + (c + 1) * kCh, rbuf[(c + 1) & 1]);
+    uint32_t pk[kCh / 2];
+#pragma unroll
+    for (int i = 0; i < kCh / 2; ++i) {
+      float2 t = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])),
+                            make_float2(c1, c1), make_float2(c0, c0));
+      const int col = col0 + c * kCh + 2 * i;
+      if constexpr (kScoreMod) {
+        t.x = fmaf(col < Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t.x);
+        t.y = fmaf(col + 1 < Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t.y);
+      }
+      float2 pr = sigmoid2_from_log2<kBF16>(t);
+      if constexpr (kMask) {
+        pr.x = (col <= lim) ? pr.x : 0.0f;
+        pr.y = (col + 1 <= lim) ? pr.y : 0.0f;
+      }
+      pk[i] = pack2<kBF16>(pr.x, pr.y);
+    }
+    tmem_st(s_addr + c * (kCh / 2), pk);
   }
-  return r;
-}
-
-// Two sigmoids at once; t holds the logits times log2(e).
-template <bool kBF16>
-__device__ __forceinline__ float2 sigmoid2_from_log2(float2 t) {
-  float2 e = make_float2(ex2_approx(-fabsf(t.x)), ex2_approx(-fabsf(t.y)));
-  const float2 r = rcp1p_poly<kBF16>(e);
-  e.x = t.x < 0.0f ? e.x : 1.0f;
-  e.y = t.y < 0.0f ? e.y : 1.0f;
-  return __fmul2_rn(e, r);
 }
 
 template <int D, bool kBF16, bool kScoreMod>
@@ -111,11 +128,13 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
                    const __grid_constant__ CUtensorMap v_map, const FwdParams p) {
   using L = FwdSmem<D>;
   constexpr int kStages = L::kStages;
+  constexpr int kSBufs = L::kSBufs;
   constexpr int kTileBytes = L::kTileBytes;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0;    // S_s at kColS + 128 s (P_s aliases its first 64 columns)
-  constexpr uint32_t kColO = 256;  // O_s at kColO + D s
+  constexpr uint32_t kColS = 0;              // S buffer i at kColS + 128 i
+  constexpr uint32_t kColO = 128 * kSBufs;   // O_s at kColO + D s
   constexpr int kSiteBase = 0x10000;
+  static_assert(kColO + 2 * D <= kTmemCols, "TMEM budget");
 
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -146,7 +165,11 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     if (p.causal) kv_end = min(kv_end, r0 + 128);
     n_kv[s] = (r0 < Lq) ? (kv_end + kTileN - 1) / kTileN : 0;
   }
-  const int n_max = max(n_kv[0], n_kv[1]);
+  const int n0 = n_kv[0], n1 = n_kv[1];
+  const int n_max = max(n0, n1);
+  // Jobs are ordered by key tile, query tile 0 before 1: (0,0) (1,0) (0,1) (1,1) ...
+  // Index of job (s, j) in that order (only meaningful when j < n_kv[s]).
+  auto job_index = [&](int s, int j) { return s == 0 ? j + min(j, n1) : j + min(j + 1, n0); };
 
   uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) + 2 * ((int64_t)b * p.o_sb + (int64_t)h * p.o_sh);
 
@@ -176,20 +199,20 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       mbar_init(bar(L::kVFull + i), 1);
       mbar_init(bar(L::kVEmpty + i), 1);
     }
-    mbar_init(bar(L::kSFull + 0), 1);
-    mbar_init(bar(L::kSFull + 1), 1);
-    mbar_init(bar(L::kPFull + 0), 128);
-    mbar_init(bar(L::kPFull + 1), 128);
+    for (int i = 0; i < kSBufs; ++i) {
+      mbar_init(bar(L::kSFull + i), 1);
+      mbar_init(bar(L::kPFull + i), 256);
+    }
     mbar_init(bar(L::kOFull), 1);
     mbar_init(bar(L::kVFix), 1);
     fence_mbar_init();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == kFwdProducerWarp && lane == 0) {
     tma_prefetch_desc(&q_map);
     tma_prefetch_desc(&k_map);
     tma_prefetch_desc(&v_map);
   }
-  if (warp == 9) {
+  if (warp == kFwdIssuerWarp) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
   }
@@ -198,7 +221,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == kFwdProducerWarp) {
     // ============================================================ TMA producer
     if (lane == 0) {
 #pragma unroll
@@ -253,153 +276,201 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         if (lane == 0) mbar_arrive(bar(L::kVFix));
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kFwdIssuerWarp) {
     // ============================================================ tcgen05 issuer
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_qk = make_idesc(128, 128, kBF16, false, false);
       constexpr uint32_t idesc_pv = make_idesc(128, D, kBF16, false, true);
-      auto issue_s = [&](int s, int st) {
-        const uint32_t qa = smem_base + L::kQOff + s * kTileBytes;
-        const uint32_t ka = smem_base + L::kKOff + st * kTileBytes;
+      const int n_jobs = n0 + n1;
+      bool ok = true;
+      // descriptor bases: Q tile 0, K stage 0 (rows = M/N, 64 contiguous elements = K) and
+      // V stage 0 (rows = K, 64 contiguous elements = N, next 64-column block 16 KB further)
+      const uint64_t q_desc0 = smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
+      const uint64_t k_desc0 = smem_desc_sw128(smem_base + L::kKOff, 16, 1024);
+      const uint64_t v_desc0 = smem_desc_sw128(smem_base + L::kVOff, 16384, 1024);
+      // cursor over the job order: (s, j) with j < n_kv[s]
+      auto advance = [&](int& s, int& j) {
+        do {
+          if (s == 0) s = 1; else { s = 0; ++j; }
+        } while (j < n_max && j >= n_kv[s]);
+      };
+      int s_s = 0, s_j = 0;  // next job whose scores are to be issued
+      if (n0 == 0) advance(s_s, s_j);
+      int p_s = s_s, p_j = s_j;  // next job whose P V product is to be issued
+      int k_seen = -1, v_seen = -1;
+#ifdef SIG_TRACE
+      long long tr_wait_p = 0, tr_wait_k = 0, tr_wait_v = 0;
+#endif
+
+      // S[buffer n % kSBufs] = Q_s K_j^T
+      auto issue_s = [&](int s, int j, int n) {
+        const int st = j % kStages;
+        if (j > k_seen) {
+          SIG_T0();
+          if (j == 0) ok = ok && mbar_wait_warp(bar(L::kQFull + s), 0, abort_flag, kSiteBase + 3);
+          ok = ok && mbar_wait_warp(bar(L::kKFull + st), (j / kStages) & 1, abort_flag, kSiteBase + 5);
+          k_seen = j;
+          SIG_TACC(tr_wait_k);
+        } else if (j == 0) {
+          ok = ok && mbar_wait_warp(bar(L::kQFull + s), 0, abort_flag, kSiteBase + 4);
+        }
+        if (!ok) return;
+        const int buf = n % kSBufs;
+        // descriptors differ from the precomputed bases only in the start-address field (>> 4)
+        const uint64_t qd = q_desc0 + (uint64_t)(s * (kTileBytes >> 4));
+        const uint64_t kd = k_desc0 + (uint64_t)(st * (kTileBytes >> 4));
+        const uint32_t dst = tmem + kColS + 128 * buf;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tmem + kColS + 128 * s, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024),
-                 idesc_qk, kk > 0);
+          const uint64_t off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          mma_ss(leader, dst, qd + off, kd + off, idesc_qk, kk > 0);
         }
+        mma_commit(leader, bar(L::kSFull + buf));
+        // last job that reads K_j: hand the stage back to the producer
+        if (s == 1 || j >= n1) mma_commit(leader, bar(L::kKEmpty + st));
       };
-      auto issue_pv = [&](int s, int st, bool first) {
-        const uint32_t va = smem_base + L::kVOff + st * kTileBytes;
+      // O_s += P[buffer n % kSBufs] V_j
+      auto issue_pv = [&](int s, int j, int n) {
+        const int st = j % kStages;
+        if (j > v_seen) {
+          SIG_T0();
+          ok = ok && mbar_wait_warp(bar(L::kVFull + st), (j / kStages) & 1, abort_flag, kSiteBase + 6);
+          if (j * kTileN + kTileN > Lk)  // padded V rows are being cleared by the producer warp
+            ok = ok && mbar_wait_warp(bar(L::kVFix), 0, abort_flag, kSiteBase + 14);
+          v_seen = j;
+          SIG_TACC(tr_wait_v);
+        }
+        const int buf = n % kSBufs;
+        {
+          SIG_T0();
+          ok = ok && mbar_wait_warp(bar(L::kPFull + buf), (n / kSBufs) & 1, abort_flag, kSiteBase + 7);
+          SIG_TACC(tr_wait_p);
+        }
+        if (!ok) return;
+        tc_fence_after_sync();
+        const uint64_t vd = v_desc0 + (uint64_t)(st * (kTileBytes >> 4));
+        const uint32_t pa = tmem + kColS + 128 * buf;
+        const uint32_t dst = tmem + kColO + D * s;
+        const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < kTileN / 16; ++kk) {
-          mma_ts(tmem + kColO + D * s, tmem + kColS + 128 * s + kk * 8, smem_desc_sw128(va + kk * 2048, 16384, 1024),
-                 idesc_pv, (!first || kk > 0) ? 1u : 0u);
+          // P of key columns [64g, 64g+64) sits, 16-bit packed, in buffer columns 64g + [0,32)
+          mma_ts(leader, dst, pa + 64 * (kk >> 2) + 8 * (kk & 3), vd + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
+                 kk > 0 ? 1u : acc0);
         }
+        if (s == 1 || j >= n1) mma_commit(leader, bar(L::kVEmpty + st));
       };
-      bool ok = true;
-      if (n_kv[0] > 0) ok = ok && mbar_wait(bar(L::kQFull + 0), 0, abort_flag, kSiteBase + 3);
-      if (n_kv[1] > 0) ok = ok && mbar_wait(bar(L::kQFull + 1), 0, abort_flag, kSiteBase + 4);
-      ok = ok && mbar_wait(bar(L::kKFull + 0), 0, abort_flag, kSiteBase + 5);
-      if (ok) {
-        if (n_kv[0] > 0) { issue_s(0, 0); mma_commit(bar(L::kSFull + 0)); }
-        if (n_kv[1] > 0) { issue_s(1, 0); mma_commit(bar(L::kSFull + 1)); }
-        mma_commit(bar(L::kKEmpty + 0));
+
+#ifdef SIG_TRACE
+      const long long tr_begin = clock64();
+#endif
+      int n_s = 0;
+      for (; n_s < kSBufs && n_s < n_jobs && ok; ++n_s) {
+        issue_s(s_s, s_j, n_s);
+        advance(s_s, s_j);
       }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
-        const int st_n = (j + 1) % kStages;
-        const uint32_t ph_n = ((j + 1) / kStages) & 1;
-        ok = mbar_wait(bar(L::kVFull + st), ph, abort_flag, kSiteBase + 6);
-        if (!ok) break;
-        if (j * kTileN + kTileN > Lk) {  // padded V rows are being cleared by the producer warp
-          ok = mbar_wait(bar(L::kVFix), 0, abort_flag, kSiteBase + 14);
-          if (!ok) break;
+      for (int n = 0; n < n_jobs && ok; ++n) {
+        issue_pv(p_s, p_j, n);
+        advance(p_s, p_j);
+        if (n_s < n_jobs && ok) {
+          issue_s(s_s, s_j, n_s);  // reuses the buffer the product above has just consumed
+          advance(s_s, s_j);
+          ++n_s;
         }
-        if (j < n_kv[0]) {
-          ok = mbar_wait(bar(L::kPFull + 0), j & 1, abort_flag, kSiteBase + 7);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_pv(0, st, j == 0);
-        }
-        if (j + 1 < n_max) {
-          ok = mbar_wait(bar(L::kKFull + st_n), ph_n, abort_flag, kSiteBase + 8);
-          if (!ok) break;
-        }
-        if (j + 1 < n_kv[0]) { issue_s(0, st_n); mma_commit(bar(L::kSFull + 0)); }
-        if (j < n_kv[1]) {
-          ok = mbar_wait(bar(L::kPFull + 1), j & 1, abort_flag, kSiteBase + 9);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_pv(1, st, j == 0);
-        }
-        mma_commit(bar(L::kVEmpty + st));
-        if (j + 1 < n_kv[1]) { issue_s(1, st_n); mma_commit(bar(L::kSFull + 1)); }
-        if (j + 1 < n_max) mma_commit(bar(L::kKEmpty + st_n));
       }
-      if (ok) mma_commit(bar(L::kOFull));
+      if (ok) mma_commit(leader, bar(L::kOFull));
+#ifdef SIG_TRACE
+      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        g_trace[32] = tr_wait_p; g_trace[33] = clock64() - tr_begin; g_trace[34] = n_jobs;
+        g_trace[35] = tr_wait_k; g_trace[36] = tr_wait_v;
+      }
+#endif
     }
-  } else if (warp < 8) {
+  } else {
     // ============================================================ sigmoid groups + epilogue
-    const int s = warp >> 2;
+    const int s = warp >> 3;                              // query tile
+    const int g = (warp >> 2) & 1;                        // which half of the key columns
     const int lane_row = (warp & 3) * 32 + lane;          // TMEM lane == row within the tile
     const int row = q0 + 128 * s + lane_row;              // query index
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem + lane_addr + kColS + 128 * s;
-    const uint32_t o_addr = tmem + lane_addr + kColO + D * s;
     const float c1 = p.scale * kLog2e;
     const float c0 = (p.bias ? p.bias[b] : p.bias_scalar) * kLog2e;
     const float* sm_row = kScoreMod ? (p.score_mod + (int64_t)b * p.Tk) : nullptr;
-    uint8_t* o_row = o_base + 2 * (int64_t)row * p.o_st;
+    uint8_t* o_row = o_base + 2 * (int64_t)row * p.o_st + g * D;  // this thread's D/2 columns (16-bit)
     const int n_mine = n_kv[s];
+    // largest visible key index for this row
+    int lim = Lk - 1;
+    if (p.causal) lim = min(lim, row);
     bool ok = true;
+#ifdef SIG_TRACE
+    long long tr_wait = 0, tr_comp = 0, tr_tail = 0;
+    const long long tr_begin = clock64();
+#endif
 
     for (int j = 0; j < n_mine; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull + s), j & 1, abort_flag, kSiteBase + 10 + s));
+      const int n = job_index(s, j);
+      const int buf = n % kSBufs;
+      {
+        SIG_T0();
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull + buf), (n / kSBufs) & 1, abort_flag, kSiteBase + 10 + s));
+        SIG_TACC(tr_wait);
+      }
       if (!ok) break;
       tc_fence_after_sync();
-      const int col0 = j * kTileN;
-      // largest visible key index for this row
-      int lim = Lk - 1;
-      if (p.causal) lim = min(lim, row);
-      const bool need_mask = (col0 + kTileN > Lk) || (p.causal && col0 + kTileN - 1 > q0 + 128 * s);
-      // two register buffers: the load of chunk c+1 is in flight while chunk c is computed
-      uint32_t rbuf[2][32];
-      tmem_ld32(s_addr, rbuf[0]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t(&r)[32] = rbuf[c & 1];
-        tmem_ld_wait_for(r);
-        if (c + 1 < 4) tmem_ld32(s_addr + (c + 1) * 32, rbuf[(c + 1) & 1]);
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float2 t = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])),
-                                make_float2(c1, c1), make_float2(c0, c0));
-          const int col = col0 + c * 32 + 2 * i;
-          if constexpr (kScoreMod) {
-            t.x = fmaf(col < p.Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t.x);
-            t.y = fmaf(col + 1 < p.Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t.y);
-          }
-          float2 pr = sigmoid2_from_log2<kBF16>(t);
-          if (need_mask) {
-            pr.x = (col <= lim) ? pr.x : 0.0f;
-            pr.y = (col + 1 <= lim) ? pr.y : 0.0f;
-          }
-          pk[i] = pack2<kBF16>(pr.x, pr.y);
-        }
-        tmem_st16(s_addr + c * 16, pk);
+      const uint32_t s_addr = tmem + lane_addr + kColS + 128 * buf + 64 * g;
+      const int col0 = j * kTileN + 64 * g;
+      const bool need_mask = (col0 + 64 > Lk) || (p.causal && col0 + 63 > q0 + 128 * s);
+      // the predicate code exists only in the instantiation used by boundary tiles
+      {
+        SIG_T0();
+        if (need_mask)
+          fwd_sigmoid_half_tile<kBF16, kScoreMod, true>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
+        else
+          fwd_sigmoid_half_tile<kBF16, kScoreMod, false>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
+        SIG_TACC(tr_comp);
       }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      mbar_arrive(bar(L::kPFull + s));
+      {
+        SIG_T0();
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(bar(L::kPFull + buf));
+        SIG_TACC(tr_tail);
+      }
     }
 
+#ifdef SIG_TRACE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0) {
+      long long* tr = g_trace + (warp >> 2) * 4;
+      tr[0] = tr_wait; tr[1] = tr_comp; tr[2] = tr_tail; tr[3] = clock64() - tr_begin;
+    }
+#endif
     if (n_mine == 0) {
       // this tile is entirely padding (or beyond Tq): zero rows
       if (row < p.Tq) {
 #pragma unroll
-        for (int c = 0; c < D * 2 / 16; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < D / 16; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
       }
     } else if (ok) {
       ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kOFull), 0, abort_flag, kSiteBase + 12));
       if (ok) {
         tc_fence_after_sync();
+        const uint32_t o_addr = tmem + lane_addr + kColO + D * s + g * (D / 2);
         const bool live = row < Lq;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < D / 64; ++c) {
           uint32_t r[32];
           tmem_ld32_sync(o_addr + c * 32, r);
           if (row < p.Tq) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
+            for (int q4 = 0; q4 < 4; ++q4) {
               uint4 w;
-              w.x = pack2<kBF16>(__uint_as_float(r[8 * g + 0]), __uint_as_float(r[8 * g + 1]));
-              w.y = pack2<kBF16>(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3]));
-              w.z = pack2<kBF16>(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5]));
-              w.w = pack2<kBF16>(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7]));
+              w.x = pack2<kBF16>(__uint_as_float(r[8 * q4 + 0]), __uint_as_float(r[8 * q4 + 1]));
+              w.y = pack2<kBF16>(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3]));
+              w.z = pack2<kBF16>(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5]));
+              w.w = pack2<kBF16>(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7]));
               if (!live) w = make_uint4(0, 0, 0, 0);
-              *reinterpret_cast<uint4*>(o_row + 64 * c + 16 * g) = w;
+              *reinterpret_cast<uint4*>(o_row + 64 * c + 16 * q4) = w;
             }
           }
         }
@@ -410,7 +481,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   // ---------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kFwdIssuerWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }
