@@ -11,15 +11,31 @@
 //   P^T  = sigmoid(scale S^T + bias), dS^T = P^T (1 - P^T) dP^T        (registers)
 //   dV_j += P^T  dO_i           (TMEM x smem -> TMEM)
 //   dK_j += dS^T Q_i            (TMEM x smem -> TMEM)
-//   dQ_i  = dS K_j              (smem x smem -> TMEM), then added into an fp32 accumulator
-//                                in global memory with vector reductions
+//   dQ_i  = dS K_j              (smem x smem -> TMEM), then added into an fp32 accumulator in
+//                                global memory.  The L2 performs such reductions at full speed
+//                                only when a request covers consecutive addresses, and a warp
+//                                that reads dQ with query rows on the TMEM lanes would scatter
+//                                32 lanes over 32 rows.  So:
+//                                D = 128: the transposed product dQ^T = K^T dS^T is computed
+//                                  instead; the head dimension lies on the lanes and one
+//                                  red.global.add.f32 per query covers a full 128-byte line;
+//                                D = 64: M = 64 would idle half of the tensor core and half of
+//                                  the lanes, and staging rows in shared memory for bulk
+//                                  reductions measured slower than the plain form, so each
+//                                  thread adds its 64 bytes of a row with four
+//                                  red.global.add.v4.f32 (the reduction traffic, not the math,
+//                                  is what bounds this case).
 //
-// Warp roles (448 threads):
-//   warps 0-3   compute group 0: query columns [0,64) of the tile, one key row per thread
-//   warps 4-7   compute group 1: query columns [64,128)
-//   warps 8-11  dQ drain: TMEM -> red.global.add.f32 (one query row per thread)
-//   warp  12    TMA producer
-//   warp  13    tcgen05 issuer, owns the TMEM allocation
+// Warp roles (20 warps):
+//   warps 0-15  compute: warp w owns TMEM lanes (key rows) 32 (w & 3) .. +31 and the query
+//               columns 32 (w >> 2) .. +31 of every tile; the same warps drain dQ
+//   warp  16    TMA producer (also clears padded rows of tiles that straddle a valid length)
+//   warp  17    tcgen05 issuer A: S^T and dP^T; owns the TMEM allocation
+//   warp  18    tcgen05 issuer B: dV, dK, dQ
+//   warp  19    idle
+// Two issuing warps, because one warp's instruction stream (waits, 32 MMAs, commits per tile
+// pair) is a serial chain that otherwise bounds the kernel.  Everything the two exchange goes
+// through mbarriers: "S columns free" after dV, "dP columns free" after dK.
 // dQ = scale * accumulator is rounded to the 16-bit type by sigattn_dq_convert_kernel.
 #pragma once
 
@@ -45,7 +61,11 @@ struct BwdParams {
   int n_kvblk;
 };
 
-constexpr int kBwdThreads = 448;
+constexpr int kBwdComputeWarps = 16;
+constexpr int kBwdProducerWarp = 16;
+constexpr int kBwdIssuerA = 17;
+constexpr int kBwdIssuerB = 18;
+constexpr int kBwdThreads = 20 * 32;
 constexpr int kBwdTileKV = 128;
 constexpr int kBwdTileQ = 128;
 
@@ -62,23 +82,80 @@ struct BwdSmem {
   static constexpr int kBarOff = kDsOff + kDsBytes;
   static constexpr int kKvFull = 0;
   static constexpr int kQFull = 1;                    // [2]
-  static constexpr int kQEmpty = kQFull + kStages;    // [2]
+  static constexpr int kQEmpty = kQFull + kStages;    // [2]  both issuers release a stage
   static constexpr int kDoFull = kQEmpty + kStages;   // [2]
   static constexpr int kDoEmpty = kDoFull + kStages;  // [2]
-  static constexpr int kSFull = kDoEmpty + kStages;
-  static constexpr int kDpFull = kSFull + 1;
-  static constexpr int kPReady = kDpFull + 1;
-  static constexpr int kDsReady = kPReady + 1;
-  static constexpr int kDqFull = kDsReady + 1;
-  static constexpr int kDqEmpty = kDqFull + 1;
-  static constexpr int kDkvFull = kDqEmpty + 1;
-  static constexpr int kKvFix = kDkvFull + 1;   // padded rows of K_j zeroed
-  static constexpr int kQdoFix = kKvFix + 1;    // padded rows of the last Q_i / dO_i zeroed
+  static constexpr int kSFull = kDoEmpty + kStages;   // S^T written
+  static constexpr int kDpFull = kSFull + 1;          // dP^T written
+  static constexpr int kPReady = kDpFull + 1;         // P^T in TMEM (16 warps)
+  static constexpr int kDsReady = kPReady + 1;        // dS^T in TMEM and shared memory (16 warps)
+  static constexpr int kSFree = kDsReady + 1;         // dV has consumed P^T: S columns reusable
+  static constexpr int kDpFree = kSFree + 1;          // dK has consumed dS^T: dP columns reusable
+  static constexpr int kDqFull = kDpFree + 1;         // dQ tile complete in TMEM
+  static constexpr int kDqEmpty = kDqFull + 1;        // dQ tile read out (16 warps)
+  static constexpr int kDkvFull = kDqEmpty + 1;       // every MMA of the CTA complete
+  static constexpr int kKvFix = kDkvFull + 1;         // padded rows of K_j zeroed
+  static constexpr int kQdoFix = kKvFix + 1;          // padded rows of the last Q_i / dO_i zeroed
   static constexpr int kNumBars = kQdoFix + 1;
   static constexpr int kMiscOff = kBarOff + 8 * kNumBars;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynBytes = kTotal + 1024;
 };
+
+// Phase A of one tile for one thread: 32 scores of its key row -> probabilities (kept in pv[]
+// for phase B) and their 16-bit packing written over the first 16 of the 32 columns read.
+// q0 = query index of the first column; valid queries for this key row are [q_lo, q_hi).
+template <bool kBF16, bool kMask>
+__device__ __forceinline__ void bwd_phase_a(uint32_t s_addr, float c1, float c0, int q0, int q_lo, int q_hi,
+                                            float (&pv)[32]) {
+  uint32_t r[32];
+  tmem_ld32_sync(s_addr, r);
+  uint32_t pk[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 t = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])),
+                                make_float2(c1, c1), make_float2(c0, c0));
+    float2 pe = sigmoid2_from_log2<kBF16>(t);
+    if constexpr (kMask) {
+      const int q = q0 + 2 * i;
+      pe.x = (q >= q_lo && q < q_hi) ? pe.x : 0.0f;
+      pe.y = (q + 1 >= q_lo && q + 1 < q_hi) ? pe.y : 0.0f;
+    }
+    pv[2 * i] = pe.x;
+    pv[2 * i + 1] = pe.y;
+    pk[i] = pack2<kBF16>(pe.x, pe.y);
+  }
+  tmem_st16(s_addr, pk);
+}
+
+// Phase B: dS = P (1 - P) dP for the same 32 columns; 16-bit dS^T goes to TMEM (over the first
+// 16 dP columns read) and to the swizzled shared-memory copy the dQ GEMM reads.
+template <bool kBF16, bool kMask>
+__device__ __forceinline__ void bwd_phase_b(uint32_t dp_addr, uint32_t ds_line, uint32_t chunk0, uint32_t sw,
+                                            const float (&pv)[32]) {
+  uint32_t r[32];
+  tmem_ld32_sync(dp_addr, r);
+  uint32_t pk[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 pp = make_float2(pv[2 * i], pv[2 * i + 1]);
+    const float2 w = __ffma2_rn(make_float2(-pp.x, -pp.y), pp, pp);  // P - P^2
+    float2 d = __fmul2_rn(w, make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
+    if constexpr (kMask) {
+      d.x = (pp.x != 0.0f) ? d.x : 0.0f;  // masked elements have P exactly 0; keeps NaN/Inf padding out
+      d.y = (pp.y != 0.0f) ? d.y : 0.0f;
+    }
+    pk[i] = pack2<kBF16>(d.x, d.y);
+  }
+  tmem_st16(dp_addr, pk);
+#pragma unroll
+  for (int m = 0; m < 4; ++m) {
+    const uint32_t chunk = (chunk0 + m) ^ sw;  // 128-byte swizzle: 16-byte chunk index XOR (row & 7)
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ds_line + chunk * 16), "r"(pk[4 * m]),
+                 "r"(pk[4 * m + 1]), "r"(pk[4 * m + 2]), "r"(pk[4 * m + 3])
+                 : "memory");
+  }
+}
 
 template <int D, bool kBF16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -88,11 +165,12 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   using L = BwdSmem<D>;
   constexpr int kTileBytes = L::kTileBytes;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0;                      // S^T, 128 fp32 columns; P^T (16-bit) in columns 64g + [0,32)
-  constexpr uint32_t kColDp = 128;                   // dP^T; dS^T (16-bit) in columns 64g + [0,32)
+  constexpr uint32_t kColS = 0;             // S^T (128 fp32 columns); column group c keeps P^T in 32c + [0,16)
+  constexpr uint32_t kColDp = 128;          // dP^T; column group c keeps dS^T in 32c + [0,16)
   constexpr uint32_t kColDv = 256;
   constexpr uint32_t kColDk = 256 + D;
-  constexpr bool kDqAliased = (D == 128);            // no room left: dQ reuses the dP^T columns
+  constexpr bool kDqT = (D == 128);         // dQ^T (head dimension on lanes) instead of dQ
+  constexpr bool kDqAliased = (D == 128);   // no room left: dQ^T reuses the dP^T columns
   constexpr uint32_t kColDq = kDqAliased ? kColDp : 384;
   constexpr int kSiteBase = 0x20000;
 
@@ -118,6 +196,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   const int i_end = (Lq + kBwdTileQ - 1) / kBwdTileQ;
   const int i_begin = p.causal ? j : 0;  // query tiles that can see this key tile (top-left aligned)
   const int n_q = (kv0 < Lk) ? max(i_end - i_begin, 0) : 0;
+  const bool ragged_kv = kv0 + kBwdTileKV > Lk;
+  // only the last query tile can straddle Lq
+  const bool ragged_last_q = (i_begin + n_q) * kBwdTileQ > Lq;
 
   uint8_t* dk_base = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((int64_t)b * p.dk_sb + (int64_t)h * p.dk_sh);
   uint8_t* dv_base = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((int64_t)b * p.dv_sb + (int64_t)h * p.dv_sh);
@@ -143,28 +224,30 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     mbar_init(bar(L::kKvFull), 1);
     for (int i = 0; i < L::kStages; ++i) {
       mbar_init(bar(L::kQFull + i), 1);
-      mbar_init(bar(L::kQEmpty + i), 1);
+      mbar_init(bar(L::kQEmpty + i), 2);   // S^T (issuer A) and dK (issuer B) both read Q_i
       mbar_init(bar(L::kDoFull + i), 1);
-      mbar_init(bar(L::kDoEmpty + i), 1);
+      mbar_init(bar(L::kDoEmpty + i), 2);  // dP^T (issuer A) and dV (issuer B) both read dO_i
     }
     mbar_init(bar(L::kSFull), 1);
     mbar_init(bar(L::kDpFull), 1);
-    mbar_init(bar(L::kPReady), 256);
-    mbar_init(bar(L::kDsReady), 256);
+    mbar_init(bar(L::kPReady), kBwdComputeWarps);
+    mbar_init(bar(L::kDsReady), kBwdComputeWarps);
+    mbar_init(bar(L::kSFree), 1);
+    mbar_init(bar(L::kDpFree), 1);
     mbar_init(bar(L::kDqFull), 1);
-    mbar_init(bar(L::kDqEmpty), 128);
+    mbar_init(bar(L::kDqEmpty), kBwdComputeWarps);
     mbar_init(bar(L::kDkvFull), 1);
     mbar_init(bar(L::kKvFix), 1);
     mbar_init(bar(L::kQdoFix), 1);
     fence_mbar_init();
   }
-  if (warp == 12 && lane == 0) {
+  if (warp == kBwdProducerWarp && lane == 0) {
     tma_prefetch_desc(&q_map);
     tma_prefetch_desc(&k_map);
     tma_prefetch_desc(&v_map);
     tma_prefetch_desc(&do_map);
   }
-  if (warp == 13) {
+  if (warp == kBwdIssuerA) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
   }
@@ -173,7 +256,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 12) {
+  if (warp == kBwdProducerWarp) {
     // ============================================================ TMA producer
     // Rows beyond the valid lengths may hold anything (NaN included).  Masked probabilities are
     // exactly zero, but 0 * NaN is NaN inside an MMA, so the padded rows of every tile that is
@@ -196,20 +279,11 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       }
     }
     bool ok = true;
-    if (kv0 + kBwdTileKV > Lk) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kKvFull), 0, abort_flag, kSiteBase + 17));
-      if (ok) {
-        zero_rows(smem_gen + L::kKOff, Lk - kv0);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kKvFix));
-      }
-    }
     for (int t = 0; t < n_q && ok; ++t) {
       const int st = t & 1;
       const uint32_t ph = (t >> 1) & 1;
       const int qrow = (i_begin + t) * kBwdTileQ;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kQEmpty + st), ph ^ 1, abort_flag, kSiteBase + 1));
+      ok = mbar_wait_warp(bar(L::kQEmpty + st), ph ^ 1, abort_flag, kSiteBase + 1);
       if (!ok) break;
       if (lane == 0) {
         mbar_expect_tx(bar(L::kQFull + st), kTileBytes);
@@ -217,7 +291,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         for (int c = 0; c < D / 64; ++c)
           tma_load_4d(smem_base + L::kQOff + st * kTileBytes + c * 16384, &q_map, bar(L::kQFull + st), c * 64, h, qrow, b);
       }
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kDoEmpty + st), ph ^ 1, abort_flag, kSiteBase + 2));
+      ok = mbar_wait_warp(bar(L::kDoEmpty + st), ph ^ 1, abort_flag, kSiteBase + 2);
       if (!ok) break;
       if (lane == 0) {
         mbar_expect_tx(bar(L::kDoFull + st), kTileBytes);
@@ -225,9 +299,17 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         for (int c = 0; c < D / 64; ++c)
           tma_load_4d(smem_base + L::kDoOff + st * kTileBytes + c * 16384, &do_map, bar(L::kDoFull + st), c * 64, h, qrow, b);
       }
-      if (qrow + kBwdTileQ > Lq) {  // only the last query tile can straddle Lq
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kQFull + st), ph, abort_flag, kSiteBase + 18));
-        ok = ok && __all_sync(0xffffffffu, mbar_wait(bar(L::kDoFull + st), ph, abort_flag, kSiteBase + 19));
+      if (t == 0 && ragged_kv) {
+        ok = mbar_wait_warp(bar(L::kKvFull), 0, abort_flag, kSiteBase + 17);
+        if (!ok) break;
+        zero_rows(smem_gen + L::kKOff, Lk - kv0);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kKvFix));
+      }
+      if (qrow + kBwdTileQ > Lq) {
+        ok = mbar_wait_warp(bar(L::kQFull + st), ph, abort_flag, kSiteBase + 18);
+        ok = ok && mbar_wait_warp(bar(L::kDoFull + st), ph, abort_flag, kSiteBase + 19);
         if (!ok) break;
         zero_rows(smem_gen + L::kQOff + st * kTileBytes, Lq - qrow);
         zero_rows(smem_gen + L::kDoOff + st * kTileBytes, Lq - qrow);
@@ -236,215 +318,234 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         if (lane == 0) mbar_arrive(bar(L::kQdoFix));
       }
     }
-  } else if (warp == 13) {
-    // ============================================================ tcgen05 issuer
-    {
-      const bool leader = elect_one();
-      constexpr uint32_t idesc_st = make_idesc(128, 128, kBF16, false, false);  // S^T, dP^T
-      constexpr uint32_t idesc_acc = make_idesc(128, D, kBF16, false, true);    // dV, dK: A in TMEM, B rows = contraction
-      constexpr uint32_t idesc_dq = make_idesc(128, D, kBF16, true, true);      // dQ: both operands row = contraction
-      const uint32_t k_s = smem_base + L::kKOff;
-      const uint32_t v_s = smem_base + L::kVOff;
-      const uint32_t ds_s = smem_base + L::kDsOff;
-      // descriptor bases; per-MMA descriptors differ only in the start-address field (>> 4)
-      const uint64_t k_km = smem_desc_sw128(k_s, 16, 1024);        // K_j, rows = M
-      const uint64_t v_km = smem_desc_sw128(v_s, 16, 1024);        // V_j, rows = M
-      const uint64_t k_mn = smem_desc_sw128(k_s, 16384, 1024);     // K_j, rows = contraction
-      const uint64_t ds_mn = smem_desc_sw128(ds_s, 16384, 1024);   // dS^T, rows = contraction
-      const uint64_t q_km0 = smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
-      const uint64_t do_km0 = smem_desc_sw128(smem_base + L::kDoOff, 16, 1024);
-      const uint64_t q_mn0 = smem_desc_sw128(smem_base + L::kQOff, 16384, 1024);
-      const uint64_t do_mn0 = smem_desc_sw128(smem_base + L::kDoOff, 16384, 1024);
-      constexpr uint64_t kStageStep = (uint64_t)(kTileBytes >> 4);
-      // C[key, query] = A[key, :] . B[query, :] over the head dimension
-      auto issue_kmajor = [&](uint32_t dcol, uint64_t a_d, uint64_t b_d) {
+  } else if (warp == kBwdIssuerA) {
+    // ============================================================ issuer A: S^T = K Q^T, dP^T = V dO^T
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_st = make_idesc(128, 128, kBF16, false, false);
+    constexpr uint32_t kStageStep = kTileBytes >> 4;
+    // operands with rows = M / N and the 64 contiguous elements = contraction
+    const uint64_t k_km = smem_desc_sw128(smem_base + L::kKOff, 16, 1024);
+    const uint64_t v_km = smem_desc_sw128(smem_base + L::kVOff, 16, 1024);
+    const uint64_t q_km0 = smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
+    const uint64_t do_km0 = smem_desc_sw128(smem_base + L::kDoOff, 16, 1024);
+    const uint32_t k_lo = (uint32_t)k_km, v_lo = (uint32_t)v_km, q_lo0 = (uint32_t)q_km0, do_lo0 = (uint32_t)do_km0;
+    const uint32_t hi = (uint32_t)(k_km >> 32);  // identical for all four (same layout parameters)
+    auto issue = [&](uint32_t dcol, uint32_t a_lo, uint32_t b_lo) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
-          mma_ss(leader, tmem + dcol, a_d + off, b_d + off, idesc_st, kk > 0);
-        }
-      };
-      // acc[key, d] += A^T[key, query] (TMEM, 16-bit) . B[query, d] (smem tile of query rows)
-      auto issue_acc = [&](uint32_t dcol, uint32_t acol, uint64_t b_d, bool first) {
-        const uint32_t acc0 = first ? 0u : 1u;
-#pragma unroll
-        for (int kk = 0; kk < kBwdTileQ / 16; ++kk) {
-          mma_ts(leader, tmem + dcol, tmem + acol + 64 * (kk >> 2) + 8 * (kk & 3), b_d + (uint64_t)(kk * (2048 >> 4)), idesc_acc,
-                 kk > 0 ? 1u : acc0);
-        }
-      };
-      auto ragged_q = [&](int t) { return (i_begin + t) * kBwdTileQ + kBwdTileQ > Lq; };
-      bool ok = mbar_wait_warp(bar(L::kKvFull), 0, abort_flag, kSiteBase + 3);
-      if (kv0 + kBwdTileKV > Lk) ok = ok && mbar_wait_warp(bar(L::kKvFix), 0, abort_flag, kSiteBase + 20);
-      ok = ok && mbar_wait_warp(bar(L::kQFull + 0), 0, abort_flag, kSiteBase + 4);
-      if (ragged_q(0)) ok = ok && mbar_wait_warp(bar(L::kQdoFix), 0, abort_flag, kSiteBase + 21);
-      if (ok) {
-        issue_kmajor(kColS, k_km, q_km0);
-        mma_commit(leader, bar(L::kSFull));
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = (uint32_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+        mma_ss(leader, tmem + dcol, make_desc(a_lo + off, hi), make_desc(b_lo + off, hi), idesc_st, kk > 0);
       }
-      ok = ok && mbar_wait_warp(bar(L::kDoFull + 0), 0, abort_flag, kSiteBase + 5);
-      if (ok) {
-        issue_kmajor(kColDp, v_km, do_km0);
-        mma_commit(leader, bar(L::kDpFull));
+    };
+    bool ok = mbar_wait_warp(bar(L::kKvFull), 0, abort_flag, kSiteBase + 3);
+    if (ragged_kv) ok = ok && mbar_wait_warp(bar(L::kKvFix), 0, abort_flag, kSiteBase + 20);
+    int st = 0;
+    uint32_t ph = 0;  // parity of the stage's "full" barriers
+    for (int t = 0; t < n_q && ok; ++t) {
+      const uint32_t prev = (uint32_t)(t - 1) & 1u;
+      ok = mbar_wait_warp(bar(L::kQFull + st), ph, abort_flag, kSiteBase + 4);
+      if (t == n_q - 1 && ragged_last_q) ok = ok && mbar_wait_warp(bar(L::kQdoFix), 0, abort_flag, kSiteBase + 21);
+      // the S columns still hold P^T of the previous tile until its dV GEMM has read them
+      if (t > 0) ok = ok && mbar_wait_warp(bar(L::kSFree), prev, abort_flag, kSiteBase + 5);
+      if (!ok) break;
+      tc_fence_after_sync();
+      issue(kColS, k_lo, q_lo0 + (uint32_t)st * kStageStep);
+      mma_commit(leader, bar(L::kSFull));
+      mma_commit(leader, bar(L::kQEmpty + st));
+      ok = mbar_wait_warp(bar(L::kDoFull + st), ph, abort_flag, kSiteBase + 6);
+      if (t > 0) {
+        // the dP columns hold dS^T of the previous tile (read by dK) and, when dQ shares them,
+        // the previous dQ tile until it has been drained
+        ok = ok && mbar_wait_warp(bar(kDqAliased ? L::kDqEmpty : L::kDpFree), prev, abort_flag, kSiteBase + 7);
       }
-      for (int t = 0; t < n_q && ok; ++t) {
-        const int st = t & 1;
-        const uint64_t q_mn = q_mn0 + st * kStageStep;
-        const uint64_t do_mn = do_mn0 + st * kStageStep;
-        const int st_n = st ^ 1;
-        const uint32_t ph_n = ((t + 1) >> 1) & 1;
-        // dV += P^T dO
-        ok = mbar_wait_warp(bar(L::kPReady), t & 1, abort_flag, kSiteBase + 6);
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_acc(kColDv, kColS, do_mn, t == 0);
-        // S^T of the next tile may overwrite P^T now
-        if (t + 1 < n_q) {
-          ok = mbar_wait_warp(bar(L::kQFull + st_n), ph_n, abort_flag, kSiteBase + 7);
-          if (ragged_q(t + 1)) ok = ok && mbar_wait_warp(bar(L::kQdoFix), 0, abort_flag, kSiteBase + 22);
-          if (!ok) break;
-          issue_kmajor(kColS, k_km, q_km0 + st_n * kStageStep);
-          mma_commit(leader, bar(L::kSFull));
-        }
-        // dK += dS^T Q
-        ok = mbar_wait_warp(bar(L::kDsReady), t & 1, abort_flag, kSiteBase + 8);
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_acc(kColDk, kColDp, q_mn, t == 0);
-        // dQ_i = dS K (needs the previous dQ tile drained out of TMEM)
-        ok = mbar_wait_warp(bar(L::kDqEmpty), (t & 1) ^ 1, abort_flag, kSiteBase + 9);
-        if (!ok) break;
-        tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
-          mma_ss(leader, tmem + kColDq, ds_mn + (uint64_t)(kk * (2048 >> 4)), k_mn + (uint64_t)(kk * (2048 >> 4)), idesc_dq,
-                 kk > 0);
-        }
-        mma_commit(leader, bar(L::kDqFull));
-        mma_commit(leader, bar(L::kQEmpty + st));
-        mma_commit(leader, bar(L::kDoEmpty + st));
-        if (t + 1 < n_q) {
-          if (kDqAliased) {
-            // dQ_i sits in the dP^T columns: wait until it has been drained
-            ok = mbar_wait_warp(bar(L::kDqEmpty), t & 1, abort_flag, kSiteBase + 10);
-            if (!ok) break;
-            tc_fence_after_sync();
-          }
-          ok = mbar_wait_warp(bar(L::kDoFull + st_n), ph_n, abort_flag, kSiteBase + 11);
-          if (!ok) break;
-          issue_kmajor(kColDp, v_km, do_km0 + st_n * kStageStep);
-          mma_commit(leader, bar(L::kDpFull));
-        }
-      }
-      if (ok) mma_commit(leader, bar(L::kDkvFull));
+      if (!ok) break;
+      tc_fence_after_sync();
+      issue(kColDp, v_lo, do_lo0 + (uint32_t)st * kStageStep);
+      mma_commit(leader, bar(L::kDpFull));
+      mma_commit(leader, bar(L::kDoEmpty + st));
+      st ^= 1;
+      if (st == 0) ph ^= 1u;
     }
-  } else if (warp < 8) {
-    // ============================================================ compute groups
-    const int g = warp >> 2;                              // which half of the query columns
-    const int lane_row = (warp & 3) * 32 + lane;          // key row within the tile == TMEM lane
+  } else if (warp == kBwdIssuerB) {
+    // ============================================================ issuer B: dV, dK, dQ
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_acc = make_idesc(128, D, kBF16, false, true);  // A in TMEM, B rows = contraction
+    // dQ (M = queries, N = D) or dQ^T (M = D, N = queries): both operands rows = contraction
+    constexpr uint32_t idesc_dq = kDqT ? make_idesc(D, 128, kBF16, true, true) : make_idesc(128, D, kBF16, true, true);
+    constexpr uint32_t kStageStep = kTileBytes >> 4;
+    // operands whose rows are the contraction index; the next 64-column block lies 16 KB further
+    const uint64_t k_mn = smem_desc_sw128(smem_base + L::kKOff, 16384, 1024);
+    const uint64_t ds_mn = smem_desc_sw128(smem_base + L::kDsOff, 16384, 1024);
+    const uint64_t q_mn0 = smem_desc_sw128(smem_base + L::kQOff, 16384, 1024);
+    const uint64_t do_mn0 = smem_desc_sw128(smem_base + L::kDoOff, 16384, 1024);
+    const uint32_t k_lo = (uint32_t)k_mn, ds_lo = (uint32_t)ds_mn, q_lo0 = (uint32_t)q_mn0, do_lo0 = (uint32_t)do_mn0;
+    const uint32_t hi = (uint32_t)(k_mn >> 32);
+    // acc[key, d] (+)= A^T[key, query] (16-bit, TMEM) . B[query, d]
+    auto issue_acc = [&](uint32_t dcol, uint32_t acol, uint32_t b_lo, uint32_t acc0) {
+#pragma unroll
+      for (int kk = 0; kk < kBwdTileQ / 16; ++kk) {
+        // queries 32c .. 32c+31 sit, 16-bit packed, in columns 32c + [0,16) of the source
+        mma_ts(leader, tmem + dcol, tmem + acol + 32 * (kk >> 1) + 8 * (kk & 1), make_desc(b_lo + kk * (2048 >> 4), hi),
+               idesc_acc, kk > 0 ? 1u : acc0);
+      }
+    };
+    bool ok = true;
+    int st = 0;
+    for (int t = 0; t < n_q && ok; ++t) {
+      const uint32_t par = (uint32_t)t & 1u;
+      const uint32_t acc0 = t > 0 ? 1u : 0u;
+      // dV += P^T dO
+      ok = mbar_wait_warp(bar(L::kPReady), par, abort_flag, kSiteBase + 8);
+      if (!ok) break;
+      tc_fence_after_sync();
+      issue_acc(kColDv, kColS, do_lo0 + (uint32_t)st * kStageStep, acc0);
+      mma_commit(leader, bar(L::kSFree));
+      mma_commit(leader, bar(L::kDoEmpty + st));
+      // dK += dS^T Q
+      ok = mbar_wait_warp(bar(L::kDsReady), par, abort_flag, kSiteBase + 9);
+      if (!ok) break;
+      tc_fence_after_sync();
+      issue_acc(kColDk, kColDp, q_lo0 + (uint32_t)st * kStageStep, acc0);
+      if (!kDqAliased) mma_commit(leader, bar(L::kDpFree));
+      mma_commit(leader, bar(L::kQEmpty + st));
+      // the dQ GEMM needs the previous dQ tile read out of its columns
+      ok = mbar_wait_warp(bar(L::kDqEmpty), par ^ 1u, abort_flag, kSiteBase + 10);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
+        const uint64_t kd = make_desc(k_lo + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
+        mma_ss(leader, tmem + kColDq, kDqT ? kd : dsd, kDqT ? dsd : kd, idesc_dq, kk > 0);
+      }
+      mma_commit(leader, bar(L::kDqFull));
+      st ^= 1;
+    }
+    if (ok) mma_commit(leader, bar(L::kDkvFull));
+  } else if (warp < kBwdComputeWarps) {
+    // ============================================================ compute warps
+    const int quarter = warp & 3;                         // TMEM lane quarter this warp may access
+    const int cg = warp >> 2;                             // query-column group: columns 32 cg .. 32 cg + 31
+    const int lane_row = quarter * 32 + lane;             // key row within the tile == TMEM lane
     const int kv = kv0 + lane_row;
-    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem + lane_addr + kColS + 64 * g;
-    const uint32_t dp_addr = tmem + lane_addr + kColDp + 64 * g;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_addr = tmem + lane_addr + kColS + 32 * cg;
+    const uint32_t dp_addr = tmem + lane_addr + kColDp + 32 * cg;
     const float c1 = p.scale * kLog2e;
     float c0 = p.bias ? p.bias[b] : p.bias_scalar;
     if (p.score_mod && kv < p.Tk) c0 += p.score_mod[(int64_t)b * p.Tk + kv];
     c0 *= kLog2e;
     const bool row_ok = kv < Lk;
-    const uint32_t ds_row = smem_base + L::kDsOff + g * 16384 + lane_row * 128;
+    // shared-memory copy of dS^T: [2 blocks of 64 queries][128 key rows][128 bytes], 128-byte swizzle
+    const uint32_t ds_line = smem_base + L::kDsOff + (cg >> 1) * 16384 + lane_row * 128;
+    const uint32_t chunk0 = (uint32_t)(cg & 1) * 4;
     const uint32_t sw = (uint32_t)(lane_row & 7);
     bool ok = true;
 
+    // ---- dQ drain (see the file header)
+    // D = 128: lane l of quarter k holds d = 32 k + l of dQ^T; this warp takes query columns 32 cg ..
+    // D = 64:  this thread holds query row `lane_row`, head columns 16 cg .. 16 cg + 15 of dQ
+    const uint32_t dq_addr = tmem + lane_addr + kColDq + (kDqT ? 32 : 16) * cg;
+    auto drain_dq = [&](int t) {  // t = local index of the query tile whose dQ is complete
+      ok = mbar_wait_warp(bar(L::kDqFull), (uint32_t)t & 1u, abort_flag, kSiteBase + 14);
+      if (!ok) return;
+      tc_fence_after_sync();
+      const int q_tile = (i_begin + t) * kBwdTileQ;
+      if constexpr (kDqT) {
+        uint32_t r[32];
+        tmem_ld32_sync(dq_addr, r);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kDqEmpty));  // the TMEM columns are free again
+#ifndef SIG_EXP_NORED
+        const int q_first = q_tile + 32 * cg;
+        float* dst = p.dq_acc + (((int64_t)b * p.Tq + q_first) * p.H + h) * D + lane_row;
+        const int64_t row_stride = (int64_t)p.H * D;
+        const int n_live = min(32, Lq - q_first);  // queries at or beyond Lq get no gradient
+#pragma unroll
+        for (int v = 0; v < 32; ++v) {
+          if (v < n_live)
+            asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + v * row_stride), "f"(__uint_as_float(r[v])) : "memory");
+        }
+#endif
+      } else {
+        uint32_t r[16];
+        tmem_ld16(dq_addr, r);
+        tmem_ld_wait_for(r);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kDqEmpty));
+#ifndef SIG_EXP_NORED
+        const int q = q_tile + lane_row;
+        if (q < Lq) {  // queries at or beyond Lq get no gradient
+          float* dst = p.dq_acc + (((int64_t)b * p.Tq + q) * p.H + h) * D + 16 * cg;
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + v4 * 4),
+                         "f"(__uint_as_float(r[4 * v4])), "f"(__uint_as_float(r[4 * v4 + 1])),
+                         "f"(__uint_as_float(r[4 * v4 + 2])), "f"(__uint_as_float(r[4 * v4 + 3]))
+                         : "memory");
+          }
+        }
+#endif
+      }
+    };
+
     for (int t = 0; t < n_q; ++t) {
-      const int qc0 = (i_begin + t) * kBwdTileQ + 64 * g;  // first query index of my columns
-      // valid(q) for this key row: q_lo <= q < Lq
+      const int q0 = (i_begin + t) * kBwdTileQ + 32 * cg;  // first query index of my columns
+      // valid queries for this key row: q_lo <= q < q_hi (empty when the key row is padding)
       const int q_lo = p.causal ? kv : 0;
-      const bool need_mask = !row_ok || (qc0 + 64 > Lq) || (p.causal && qc0 < kv0 + kBwdTileKV - 1);
-      float pv[64];
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull), t & 1, abort_flag, kSiteBase + 12));
+      const int q_hi = row_ok ? Lq : 0;
+      // warp-uniform on purpose: the two instantiations contain warp-collective TMEM accesses
+      const bool need_mask = ragged_kv || (q0 + 32 > Lq) || (p.causal && q0 < kv0 + kBwdTileKV - 1);
+      float pv[32];
+      ok = mbar_wait_warp(bar(L::kSFull), (uint32_t)t & 1u, abort_flag, kSiteBase + 12);
       if (!ok) break;
       tc_fence_after_sync();
-      uint32_t rbuf[2][32];
-      tmem_ld32(s_addr, rbuf[0]);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t(&r)[32] = rbuf[c];
-        tmem_ld_wait_for(r);
-        if (c == 0) tmem_ld32(s_addr + 32, rbuf[1]);
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 t = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])),
-                                      make_float2(c1, c1), make_float2(c0, c0));
-          float2 pe = sigmoid2_from_log2<kBF16>(t);
-          if (need_mask) {
-            const int q = qc0 + c * 32 + 2 * i;
-            pe.x = (row_ok && q >= q_lo && q < Lq) ? pe.x : 0.0f;
-            pe.y = (row_ok && q + 1 >= q_lo && q + 1 < Lq) ? pe.y : 0.0f;
-          }
-          pv[c * 32 + 2 * i] = pe.x;
-          pv[c * 32 + 2 * i + 1] = pe.y;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) pk[i] = pack2<kBF16>(pv[c * 32 + 2 * i], pv[c * 32 + 2 * i + 1]);
-        tmem_st16(s_addr + c * 16, pk);
-      }
+#ifdef SIG_EXP_BWD_NOCOMPUTE
+      if (p.Tq < 0)
+#endif
+      if (need_mask) bwd_phase_a<kBF16, true>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
+      else           bwd_phase_a<kBF16, false>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(bar(L::kPReady));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(L::kPReady));
 
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kDpFull), t & 1, abort_flag, kSiteBase + 13));
-      if (!ok) break;
+      // dQ of the previous tile is complete by now (or soon): drain it while dP^T is computed.
+      // Its completion also means the dQ GEMM no longer reads the shared-memory copy of dS.
       if (t > 0) {
-        // the shared-memory copy of dS is still being read by the previous dQ MMA until then
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kDqFull), (t - 1) & 1, abort_flag, kSiteBase + 14));
+        drain_dq(t - 1);
         if (!ok) break;
       }
+
+      ok = mbar_wait_warp(bar(L::kDpFull), (uint32_t)t & 1u, abort_flag, kSiteBase + 13);
+      if (!ok) break;
       tc_fence_after_sync();
-      tmem_ld32(dp_addr, rbuf[0]);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t(&r)[32] = rbuf[c];
-        tmem_ld_wait_for(r);
-        if (c == 0) tmem_ld32(dp_addr + 32, rbuf[1]);
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 pp = make_float2(pv[c * 32 + 2 * i], pv[c * 32 + 2 * i + 1]);
-          // dS = P (1 - P) dP = (P - P^2) dP
-          const float2 w = __ffma2_rn(make_float2(-pp.x, -pp.y), pp, pp);
-          float2 d = __fmul2_rn(w, make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
-          if (need_mask) {
-            d.x = (pp.x != 0.0f) ? d.x : 0.0f;  // masked elements have P exactly 0; keeps NaN/Inf padding out
-            d.y = (pp.y != 0.0f) ? d.y : 0.0f;
-          }
-          pk[i] = pack2<kBF16>(d.x, d.y);
-        }
-        tmem_st16(dp_addr + c * 16, pk);
-        // shared-memory copy for the dQ GEMM: row = key, 64 query columns per 128-byte swizzled line
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-          const uint32_t chunk = (uint32_t)(4 * c + m) ^ sw;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ds_row + chunk * 16), "r"(pk[4 * m]),
-                       "r"(pk[4 * m + 1]), "r"(pk[4 * m + 2]), "r"(pk[4 * m + 3])
-                       : "memory");
-        }
-      }
+#ifdef SIG_EXP_BWD_NOCOMPUTE
+      if (p.Tq < 0)
+#endif
+      if (need_mask) bwd_phase_b<kBF16, true>(dp_addr, ds_line, chunk0, sw, pv);
+      else           bwd_phase_b<kBF16, false>(dp_addr, ds_line, chunk0, sw, pv);
       fence_proxy_async_smem();
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(bar(L::kDsReady));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(L::kDsReady));
     }
+    if (ok) drain_dq(n_q - 1);
 
-    // ------------------------------------------------------------ epilogue: group 0 -> dV, group 1 -> dK
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kDkvFull), 0, abort_flag, kSiteBase + 15));
+    // ------------------------------------------------------------ epilogue
+    // column groups 0,1 store dV, groups 2,3 store dK (each half of the head dimension)
+    if (ok) ok = mbar_wait_warp(bar(L::kDkvFull), 0, abort_flag, kSiteBase + 15);
     if (ok) {
       tc_fence_after_sync();
-      const uint32_t acc_addr = tmem + lane_addr + (g == 0 ? kColDv : kColDk);
-      const float mul = (g == 0) ? 1.0f : p.scale;
-      uint8_t* out_row = (g == 0 ? dv_base + 2 * (int64_t)kv * p.dv_st : dk_base + 2 * (int64_t)kv * p.dk_st);
+      const bool is_dk = cg >= 2;
+      const int col0 = (cg & 1) * (D / 2);
+      const uint32_t acc_addr = tmem + lane_addr + (is_dk ? kColDk : kColDv) + col0;
+      const float mul = is_dk ? p.scale : 1.0f;
+      uint8_t* out_row = (is_dk ? dk_base + 2 * (int64_t)kv * p.dk_st : dv_base + 2 * (int64_t)kv * p.dv_st) + 2 * col0;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
         tmem_ld32_sync(acc_addr + c * 32, r);
         if (kv < p.Tk) {
@@ -461,43 +562,14 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         }
       }
     }
-  } else if (warp < 12) {
-    // ============================================================ dQ drain
-    const int lane_row = (warp & 3) * 32 + lane;  // query row within the tile
-    const uint32_t dq_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kColDq;
-    bool ok = true;
-    for (int t = 0; t < n_q; ++t) {
-      const int q = (i_begin + t) * kBwdTileQ + lane_row;
-      float* dst = p.dq_acc + (((int64_t)b * p.Tq + q) * p.H + h) * D;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kDqFull), t & 1, abort_flag, kSiteBase + 16));
-      if (!ok) break;
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32_sync(dq_addr + c * 32, r);
-        if (c == D / 32 - 1) {
-          // everything is in registers: hand the TMEM columns back before the slow part
-          tc_fence_before_sync();
-          mbar_arrive(bar(L::kDqEmpty));
-        }
-        if (q < Lq) {
-#pragma unroll
-          for (int v4 = 0; v4 < 8; ++v4) {
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c * 32 + v4 * 4),
-                         "f"(__uint_as_float(r[4 * v4])), "f"(__uint_as_float(r[4 * v4 + 1])),
-                         "f"(__uint_as_float(r[4 * v4 + 2])), "f"(__uint_as_float(r[4 * v4 + 3]))
-                         : "memory");
-          }
-        }
-      }
-    }
   }
+
+
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 13) {
+  if (warp == kBwdIssuerA) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
   }

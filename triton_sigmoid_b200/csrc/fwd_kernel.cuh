@@ -201,7 +201,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     }
     for (int i = 0; i < kSBufs; ++i) {
       mbar_init(bar(L::kSFull + i), 1);
-      mbar_init(bar(L::kPFull + i), 256);
+      mbar_init(bar(L::kPFull + i), 8);  // one arrival per sigmoid warp of the query tile
     }
     mbar_init(bar(L::kOFull), 1);
     mbar_init(bar(L::kVFix), 1);
@@ -241,6 +241,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const uint32_t ph = (j / kStages) & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kKEmpty + st), ph ^ 1, abort_flag, kSiteBase + 1));
       if (!ok) break;
+#ifdef SIG_EXP_NOLOAD
+      if (lane == 0 && j >= kStages) mbar_arrive(bar(L::kKFull + st)); else
+#endif
       if (lane == 0) {
         mbar_expect_tx(bar(L::kKFull + st), kTileBytes);
 #pragma unroll
@@ -250,6 +253,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       }
       ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kVEmpty + st), ph ^ 1, abort_flag, kSiteBase + 2));
       if (!ok) break;
+#ifdef SIG_EXP_NOLOAD
+      if (lane == 0 && j >= kStages) mbar_arrive(bar(L::kVFull + st)); else
+#endif
       if (lane == 0) {
         mbar_expect_tx(bar(L::kVFull + st), kTileBytes);
 #pragma unroll
@@ -278,112 +284,124 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     }
   } else if (warp == kFwdIssuerWarp) {
     // ============================================================ tcgen05 issuer
+    // This warp's instruction stream is one long dependent chain, so its length per job decides
+    // how quickly finished probabilities turn into new scores: all ring positions, stage numbers
+    // and barrier parities are carried incrementally (no division, no modulo), and descriptors
+    // are a precomputed base plus a constant in the start-address field.
     {
       const bool leader = elect_one();
       constexpr uint32_t idesc_qk = make_idesc(128, 128, kBF16, false, false);
       constexpr uint32_t idesc_pv = make_idesc(128, D, kBF16, false, true);
+      constexpr uint32_t kStageStep = kTileBytes >> 4;  // one smem stage, in descriptor address units
       const int n_jobs = n0 + n1;
       bool ok = true;
-      // descriptor bases: Q tile 0, K stage 0 (rows = M/N, 64 contiguous elements = K) and
-      // V stage 0 (rows = K, 64 contiguous elements = N, next 64-column block 16 KB further)
+      // Q tile 0, K stage 0 (rows = M/N, the 64 contiguous elements = K) and V stage 0 (rows = K,
+      // the 64 contiguous elements = N, next 64-column block 16 KB further)
       const uint64_t q_desc0 = smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
       const uint64_t k_desc0 = smem_desc_sw128(smem_base + L::kKOff, 16, 1024);
       const uint64_t v_desc0 = smem_desc_sw128(smem_base + L::kVOff, 16384, 1024);
-      // cursor over the job order: (s, j) with j < n_kv[s]
-      auto advance = [&](int& s, int& j) {
-        do {
-          if (s == 0) s = 1; else { s = 0; ++j; }
-        } while (j < n_max && j >= n_kv[s]);
-      };
-      int s_s = 0, s_j = 0;  // next job whose scores are to be issued
-      if (n0 == 0) advance(s_s, s_j);
-      int p_s = s_s, p_j = s_j;  // next job whose P V product is to be issued
-      int k_seen = -1, v_seen = -1;
-#ifdef SIG_TRACE
-      long long tr_wait_p = 0, tr_wait_k = 0, tr_wait_v = 0;
-#endif
+      const uint32_t q_lo = (uint32_t)q_desc0, q_hi = (uint32_t)(q_desc0 >> 32);
+      const uint32_t k_lo = (uint32_t)k_desc0, k_hi = (uint32_t)(k_desc0 >> 32);
+      const uint32_t v_lo = (uint32_t)v_desc0, v_hi = (uint32_t)(v_desc0 >> 32);
 
-      // S[buffer n % kSBufs] = Q_s K_j^T
-      auto issue_s = [&](int s, int j, int n) {
-        const int st = j % kStages;
-        if (j > k_seen) {
-          SIG_T0();
-          if (j == 0) ok = ok && mbar_wait_warp(bar(L::kQFull + s), 0, abort_flag, kSiteBase + 3);
-          ok = ok && mbar_wait_warp(bar(L::kKFull + st), (j / kStages) & 1, abort_flag, kSiteBase + 5);
-          k_seen = j;
-          SIG_TACC(tr_wait_k);
-        } else if (j == 0) {
-          ok = ok && mbar_wait_warp(bar(L::kQFull + s), 0, abort_flag, kSiteBase + 4);
-        }
-        if (!ok) return;
-        const int buf = n % kSBufs;
-        // descriptors differ from the precomputed bases only in the start-address field (>> 4)
-        const uint64_t qd = q_desc0 + (uint64_t)(s * (kTileBytes >> 4));
-        const uint64_t kd = k_desc0 + (uint64_t)(st * (kTileBytes >> 4));
-        const uint32_t dst = tmem + kColS + 128 * buf;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
-          mma_ss(leader, dst, qd + off, kd + off, idesc_qk, kk > 0);
-        }
-        mma_commit(leader, bar(L::kSFull + buf));
-        // last job that reads K_j: hand the stage back to the producer
-        if (s == 1 || j >= n1) mma_commit(leader, bar(L::kKEmpty + st));
+      // Cursor over the job order (0,0) (1,0) (0,1) (1,1) ... restricted to j < n_kv[s].
+      struct Cursor {
+        int s, j;         // query tile, key tile
+        int st;           // smem stage of key tile j
+        uint32_t ph;      // parity of that stage's "full" barrier
+        int buf;          // S buffer of the job
+        uint32_t bph;     // parity of that buffer's barriers
+        bool fresh;       // first job that touches key tile j
       };
-      // O_s += P[buffer n % kSBufs] V_j
-      auto issue_pv = [&](int s, int j, int n) {
-        const int st = j % kStages;
-        if (j > v_seen) {
-          SIG_T0();
-          ok = ok && mbar_wait_warp(bar(L::kVFull + st), (j / kStages) & 1, abort_flag, kSiteBase + 6);
-          if (j * kTileN + kTileN > Lk)  // padded V rows are being cleared by the producer warp
-            ok = ok && mbar_wait_warp(bar(L::kVFix), 0, abort_flag, kSiteBase + 14);
-          v_seen = j;
-          SIG_TACC(tr_wait_v);
+      auto advance = [&](Cursor& c) {
+        if (c.s == 0 && c.j < n1) {
+          c.s = 1;
+          c.fresh = false;
+        } else {
+          ++c.j;
+          c.s = (c.j < n0) ? 0 : 1;
+          if (++c.st == kStages) { c.st = 0; c.ph ^= 1u; }
+          c.fresh = true;
         }
-        const int buf = n % kSBufs;
+        if (++c.buf == kSBufs) { c.buf = 0; c.bph ^= 1u; }
+      };
+      Cursor cs{(n0 > 0) ? 0 : 1, 0, 0, 0u, 0, 0u, true};  // next scores to issue
+      Cursor cp = cs;                                      // next P V product to issue
+
+#ifdef SIG_TRACE
+      long long tr_wait = 0, tr_mma = 0;
+      const long long tr_begin = clock64();
+#endif
+      // S[buf] = Q_s K_j^T
+      auto issue_s = [&](const Cursor& c) {
         {
           SIG_T0();
-          ok = ok && mbar_wait_warp(bar(L::kPFull + buf), (n / kSBufs) & 1, abort_flag, kSiteBase + 7);
-          SIG_TACC(tr_wait_p);
+          if (c.j == 0) ok = ok && mbar_wait_warp(bar(L::kQFull + c.s), 0, abort_flag, kSiteBase + 3);
+          if (c.fresh) ok = ok && mbar_wait_warp(bar(L::kKFull + c.st), c.ph, abort_flag, kSiteBase + 5);
+          SIG_TACC(tr_wait);
         }
         if (!ok) return;
+        SIG_T0();
+        const uint32_t qa = q_lo + (uint32_t)c.s * kStageStep;
+        const uint32_t ka = k_lo + (uint32_t)c.st * kStageStep;
+        const uint32_t dst = tmem + kColS + 128u * (uint32_t)c.buf;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (uint32_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          mma_ss(leader, dst, make_desc(qa + off, q_hi), make_desc(ka + off, k_hi), idesc_qk, kk > 0);
+        }
+        mma_commit(leader, bar(L::kSFull + c.buf));
+        // last job that reads K_j: hand the stage back to the producer
+        if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kKEmpty + c.st));
+        SIG_TACC(tr_mma);
+      };
+      // O_s += P[buf] V_j
+      auto issue_pv = [&](const Cursor& c) {
+        {
+          SIG_T0();
+          if (c.fresh) {
+            ok = ok && mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
+            if (c.j * kTileN + kTileN > Lk)  // padded V rows are being cleared by the producer warp
+              ok = ok && mbar_wait_warp(bar(L::kVFix), 0, abort_flag, kSiteBase + 14);
+          }
+          ok = ok && mbar_wait_warp(bar(L::kPFull + c.buf), c.bph, abort_flag, kSiteBase + 7);
+          SIG_TACC(tr_wait);
+        }
+        if (!ok) return;
+        SIG_T0();
         tc_fence_after_sync();
-        const uint64_t vd = v_desc0 + (uint64_t)(st * (kTileBytes >> 4));
-        const uint32_t pa = tmem + kColS + 128 * buf;
-        const uint32_t dst = tmem + kColO + D * s;
-        const uint32_t acc0 = j > 0 ? 1u : 0u;
+        const uint32_t va = v_lo + (uint32_t)c.st * kStageStep;
+        const uint32_t pa = tmem + kColS + 128u * (uint32_t)c.buf;
+        const uint32_t dst = tmem + kColO + (uint32_t)(D * c.s);
+        const uint32_t acc0 = c.j > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < kTileN / 16; ++kk) {
           // P of key columns [64g, 64g+64) sits, 16-bit packed, in buffer columns 64g + [0,32)
-          mma_ts(leader, dst, pa + 64 * (kk >> 2) + 8 * (kk & 3), vd + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
+          mma_ts(leader, dst, pa + 64 * (kk >> 2) + 8 * (kk & 3), make_desc(va + kk * (2048 >> 4), v_hi), idesc_pv,
                  kk > 0 ? 1u : acc0);
         }
-        if (s == 1 || j >= n1) mma_commit(leader, bar(L::kVEmpty + st));
+        if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
+        SIG_TACC(tr_mma);
       };
 
-#ifdef SIG_TRACE
-      const long long tr_begin = clock64();
-#endif
       int n_s = 0;
       for (; n_s < kSBufs && n_s < n_jobs && ok; ++n_s) {
-        issue_s(s_s, s_j, n_s);
-        advance(s_s, s_j);
+        issue_s(cs);
+        advance(cs);
       }
       for (int n = 0; n < n_jobs && ok; ++n) {
-        issue_pv(p_s, p_j, n);
-        advance(p_s, p_j);
+        issue_pv(cp);
+        advance(cp);
         if (n_s < n_jobs && ok) {
-          issue_s(s_s, s_j, n_s);  // reuses the buffer the product above has just consumed
-          advance(s_s, s_j);
+          issue_s(cs);  // reuses the buffer the product above has just consumed
+          advance(cs);
           ++n_s;
         }
       }
       if (ok) mma_commit(leader, bar(L::kOFull));
 #ifdef SIG_TRACE
-      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-        g_trace[32] = tr_wait_p; g_trace[33] = clock64() - tr_begin; g_trace[34] = n_jobs;
-        g_trace[35] = tr_wait_k; g_trace[36] = tr_wait_v;
+      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) {
+        g_trace[32] = tr_wait; g_trace[33] = clock64() - tr_begin; g_trace[34] = n_jobs; g_trace[35] = tr_mma;
       }
 #endif
     }
@@ -424,6 +442,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       // the predicate code exists only in the instantiation used by boundary tiles
       {
         SIG_T0();
+#ifdef SIG_EXP_NOSIGMOID
+        if (p.Tq < 0)
+#endif
         if (need_mask)
           fwd_sigmoid_half_tile<kBF16, kScoreMod, true>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
         else
@@ -434,7 +455,8 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         SIG_T0();
         tmem_st_wait();
         tc_fence_before_sync();
-        mbar_arrive(bar(L::kPFull + buf));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kPFull + buf));  // 256 arrivals on one barrier would serialise
         SIG_TACC(tr_tail);
       }
     }

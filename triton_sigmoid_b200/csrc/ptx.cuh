@@ -131,6 +131,11 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
   return d;
 }
 
+// Reassemble a descriptor from its halves (arithmetic on the start address touches only `lo`).
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
 // Instruction descriptor for kind::f16 (fp16 / bf16 inputs, fp32 accumulate).
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N, bool bf16, bool a_mn_major, bool b_mn_major) {
   return (1u << 4)                          // D format fp32
