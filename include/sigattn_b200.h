@@ -94,6 +94,29 @@ int sigattn_fwd(const SigAttnParams *p);
  * >= seq_lens_k[b] are written as zeros.  The fp32 dQ accumulator lives in `workspace`. */
 int sigattn_bwd(const SigAttnParams *p);
 
+/* Backward pass for callers that cannot hand the library a workspace.  (No counterpart in the
+ * reference: its backward needs no scratch memory because it recomputes S in two kernels.)
+ *
+ * Some hosts of this library are not allowed to allocate device memory at the moment they call
+ * it: a plugin running inside an inference server or a framework whose memory pool is fixed at
+ * start-up, code between the begin and end of a stream capture, a real-time loop that must not
+ * enter the driver's allocator.  For them this entry point keeps the fp32 dQ accumulator in a
+ * fixed array inside the library's own device image (SIGATTN_STATIC_SCRATCH_ELEMS floats, 32 MiB,
+ * resident on every GPU that loads the library until the process exits) and ignores
+ * p->workspace / p->workspace_bytes.  Everything else - inputs, outputs, semantics, results - is
+ * as for sigattn_bwd.  It calls no cudaMalloc / cudaFree or other allocating routine.
+ *
+ *  - Limit: B * Tq * H * D <= SIGATTN_STATIC_SCRATCH_ELEMS, otherwise the call is rejected
+ *    (negative return, message from sigattn_last_error()) before anything is launched.
+ *  - The first call on each device looks up the device address of the array; make that first
+ *    call outside any stream capture.
+ *  - All calls on one device share the one array.  Each call zero-fills the part it uses on
+ *    p->stream before its kernels run, so leftovers of earlier calls never matter; but two calls
+ *    whose GPU work overlaps in time (different streams, no dependency) race on it.  Serialise
+ *    them on one stream or with events. */
+#define SIGATTN_STATIC_SCRATCH_ELEMS (8u * 1024u * 1024u)
+int sigattn_bwd_static_scratch(const SigAttnParams *p);
+
 /* Bytes of `workspace` sigattn_bwd needs for this problem (fp32 dQ accumulator). */
 size_t sigattn_bwd_workspace_bytes(int32_t B, int32_t Tq, int32_t H, int32_t D);
 

@@ -15,12 +15,14 @@ from .build import LIB_PATH
 SIGATTN_FP16 = 0
 SIGATTN_BF16 = 1
 SIGATTN_CAUSAL = 1
+SIGATTN_STATIC_SCRATCH_ELEMS = 8 * 1024 * 1024
 
 Q_ABI_VERSION, Q_SM_ARCH, Q_MAX_HEAD_DIM, Q_PARAMS_SIZE = 0, 1, 2, 3
 
 EXPORTED_SYMBOLS = (
     "sigattn_fwd",
     "sigattn_bwd",
+    "sigattn_bwd_static_scratch",
     "sigattn_bwd_workspace_bytes",
     "sigattn_last_error",
     "sigattn_query",
@@ -95,6 +97,8 @@ def load() -> ctypes.CDLL:
         lib.sigattn_fwd.restype = ctypes.c_int
         lib.sigattn_bwd.argtypes = [ctypes.POINTER(SigAttnParams)]
         lib.sigattn_bwd.restype = ctypes.c_int
+        lib.sigattn_bwd_static_scratch.argtypes = [ctypes.POINTER(SigAttnParams)]
+        lib.sigattn_bwd_static_scratch.restype = ctypes.c_int
         lib.sigattn_bwd_workspace_bytes.argtypes = [ctypes.c_int32] * 4
         lib.sigattn_bwd_workspace_bytes.restype = ctypes.c_size_t
         lib.sigattn_last_error.argtypes = []

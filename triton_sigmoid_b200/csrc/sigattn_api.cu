@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
+#include <mutex>
 #include <stdio.h>
 #include <string.h>
 
@@ -208,6 +209,31 @@ int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   return 0;
 }
 
+// Scratch of sigattn_bwd_static_scratch: lives in the device image of this library.
+static __device__ __align__(256) float g_static_dq_scratch[SIGATTN_STATIC_SCRATCH_ELEMS];
+
+// In host code the name above is only a handle for the runtime, not a device address; the
+// address valid on `device` is looked up once per device (with that device current) and cached.
+int static_scratch_ptr(int device, float** out) {
+  constexpr int kMaxDevices = 64;
+  static float* cached[kMaxDevices] = {};
+  static std::mutex mu;
+  if (device < 0 || device >= kMaxDevices) return fail(-2, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[device]) {
+    int cur = -1;
+    SIG_CUDA(cudaGetDevice(&cur));
+    if (cur != device) return fail(-100, "internal: device %d is not current (current is %d)", device, cur);
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_dq_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(-100, "cudaGetSymbolAddress(static dQ scratch) failed on device %d: %s", device, cudaGetErrorString(e));
+    cached[device] = ptr;
+  }
+  *out = cached[device];
+  return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -310,6 +336,29 @@ int sigattn_bwd(const SigAttnParams* p) {
   }
   if (p->D == 64) return p->dtype == SIGATTN_BF16 ? launch_bwd<64, true>(p, qm, km, vm, dom) : launch_bwd<64, false>(p, qm, km, vm, dom);
   return p->dtype == SIGATTN_BF16 ? launch_bwd<128, true>(p, qm, km, vm, dom) : launch_bwd<128, false>(p, qm, km, vm, dom);
+}
+
+int sigattn_bwd_static_scratch(const SigAttnParams* p) {
+  g_err[0] = 0;
+  int rc = check_common(p, true);
+  if (rc < 0) return rc;
+  if (rc == 1) return 0;
+  const unsigned long long elems = (unsigned long long)p->B * (unsigned long long)p->Tq * (unsigned long long)p->H *
+                                   (unsigned long long)p->D;
+  if (elems > SIGATTN_STATIC_SCRATCH_ELEMS)
+    return fail(-4, "problem too large for the built-in scratch: B*Tq*H*D = %llu elements, limit %u; "
+                    "use sigattn_bwd with a caller-provided workspace", elems, (unsigned)SIGATTN_STATIC_SCRATCH_ELEMS);
+  float* scratch = nullptr;
+  {
+    DeviceGuard g;  // makes p->device current for the address lookup
+    SIG_CUDA(g.enter(p->device));
+    if ((rc = static_scratch_ptr(p->device, &scratch))) return rc;
+  }
+  // Same path as sigattn_bwd from here on; it zero-fills the accumulator on p->stream first.
+  SigAttnParams q = *p;
+  q.workspace = scratch;
+  q.workspace_bytes = (size_t)SIGATTN_STATIC_SCRATCH_ELEMS * sizeof(float);
+  return sigattn_bwd(&q);
 }
 
 }  // extern "C"
