@@ -407,11 +407,19 @@ def main():
         time_main_kernel("bwd", qd, kd, vd, do, **dict(kw, iters=3))
         kb = statistics.mean(time_main_kernel("bwd", qd, kd, vd, do, **kw))
         kf = statistics.mean(time_main_kernel("fwd", qd, kd, vd, **kw))
+        # DRAM bytes per (batch, token, head, d) element of one launch, from an ncu capture of a
+        # B=2 case of this workload (profiles/ncu_full_fwd_bwd_fp16_N4096_D64.md: backward 100.7 MB
+        # read + 24.6 MB written, forward 50.4 + 2.0 MB, for 2*4096*16*64 elements); DRAM traffic grows
+        # in proportion to the element count, so it is scaled to this launch.
+        elems = float(wl["B"]) * w["N"] * wl["H"] * w["D"]
+        traffic_bwd = 14.94 * elems if (w["D"] == 64 and not w["padded"]) else None
+        traffic_fwd = 6.24 * elems if (w["D"] == 64 and not w["padded"]) else None
         ach = 2.5 * F / (kb * 1e-3) / 1e12
         line["roofline"] = {"bound": "tensor", "kernel": "sigattn_bwd_kernel", "achieved": ach, "peak": pk["burst"],
-                            "unit": "TFLOP/s", "frac": ach / pk["burst"], "traffic": None,
+                            "unit": "TFLOP/s", "frac": ach / pk["burst"], "traffic": traffic_bwd,
+                            "algorithmic_bytes": 14.0 * elems,
                             "peak_source": f"{pk['source']} bf16 cuBLAS burst", "ms_per_launch": kb,
-                            "fwd_kernel": {"achieved": F / (kf * 1e-3) / 1e12, "frac": F / (kf * 1e-3) / 1e12 / pk["burst"],
+                            "fwd_kernel": {"traffic": traffic_fwd, "algorithmic_bytes": 8.0 * elems, "achieved": F / (kf * 1e-3) / 1e12, "frac": F / (kf * 1e-3) / 1e12 / pk["burst"],
                                            "ms_per_launch": kf}}
         # kernels of this library per timed step: forward, backward, dQ convert
         line["gpu_launches"] = 3 * args.steps
