@@ -5,13 +5,14 @@
 // (src/triton_sigmoid/sigmoid_triton_dense.py:23-154) and _fwd_padded_kernel
 // (src/triton_sigmoid/sigmoid_triton_padded.py:24-171).
 //
-// Structure (sm_100a, 18 warps):
+// Structure (sm_100a, 20 warps):
 //   warps 0-7    sigmoid groups of query tile 0 (rows [q0, q0+128)): warps 0-3 take key columns
 //                [0,64) of every score tile, warps 4-7 columns [64,128); one thread per row
 //   warps 8-15   the same for query tile 1 (rows [q0+128, q0+256))
 //   warp  16     TMA producer: Q tiles once, then K_j / V_j through a ring of smem stages
-//   warp  17     tcgen05 issuer: S = Q_s K_j^T (smem x smem -> TMEM fp32) and
-//                O_s += P V_j (TMEM x smem -> TMEM fp32); also owns the TMEM allocation
+//   warp  17     tcgen05 issuer 1: S = Q_s K_j^T (smem x smem -> TMEM fp32); owns the TMEM allocation
+//   warp  18     tcgen05 issuer 2: O_s += P V_j (TMEM x smem -> TMEM fp32)
+//   warp  19     idle
 // There is no row normaliser in sigmoid attention, so O simply accumulates in TMEM over the
 // whole key loop.  The (query tile, key tile) jobs are processed in a fixed order through a
 // small ring of S buffers in TMEM (3 when D = 64, 2 when D = 128): the issuer computes the
@@ -55,8 +56,9 @@ __device__ long long g_trace[64];
 #endif
 constexpr int kFwdSigmoidWarps = 16;
 constexpr int kFwdProducerWarp = 16;
-constexpr int kFwdIssuerWarp = 17;
-constexpr int kFwdThreads = 18 * 32;
+constexpr int kFwdIssuerWarp = 17;   // S = Q K^T, owns the TMEM allocation
+constexpr int kFwdIssuerWarp2 = 18;  // O += P V
+constexpr int kFwdThreads = 20 * 32;
 constexpr int kFwdBlockM = 256;  // query rows per CTA (two 128-row tiles)
 constexpr int kTileN = 128;      // key rows per step
 
@@ -79,10 +81,34 @@ struct FwdSmem {
   static constexpr int kPFull = kSFull + kSBufs;      // [kSBufs]
   static constexpr int kOFull = kPFull + kSBufs;      // [1]
   static constexpr int kVFix = kOFull + 1;            // [1] padded rows of the last V tile zeroed
-  static constexpr int kNumBars = kVFix + 1;
+  static constexpr int kPvDone = kVFix + 1;           // [kSBufs] P V product of the buffer's job complete
+  static constexpr int kNumBars = kPvDone + kSBufs;
   static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int)
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynBytes = kTotal + 1024;  // slack to align the base to 1024 bytes
+};
+
+// Cursor over the job order (0,0) (1,0) (0,1) (1,1) ... restricted to j < n_kv[s], with
+// everything an issuing warp needs about the job carried along incrementally.
+struct FwdCursor {
+  int s, j;     // query tile, key tile
+  int st;       // smem stage of key tile j
+  uint32_t ph;  // parity of that stage's "full" barrier
+  int buf;      // S buffer of the job
+  uint32_t bph; // parity of that buffer's barriers
+  bool fresh;   // first job that touches key tile j
+  __device__ __forceinline__ void advance(int n0, int n1, int n_stages, int n_bufs) {
+    if (s == 0 && j < n1) {
+      s = 1;
+      fresh = false;
+    } else {
+      ++j;
+      s = (j < n0) ? 0 : 1;
+      if (++st == n_stages) { st = 0; ph ^= 1u; }
+      fresh = true;
+    }
+    if (++buf == n_bufs) { buf = 0; bph ^= 1u; }
+  }
 };
 
 // Turns 64 score columns of one TMEM lane (this thread's query row) into 16-bit probabilities,
@@ -134,6 +160,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   constexpr uint32_t kColS = 0;              // S buffer i at kColS + 128 i
   constexpr uint32_t kColO = 128 * kSBufs;   // O_s at kColO + D s
   constexpr int kSiteBase = 0x10000;
+  // D = 64: scores and P V are issued by two warps (the issue stream bounds the kernel); D = 128:
+  // one warp issues both, in order - with only two S buffers the extra barrier hop costs more
+  constexpr bool kSplitIssue = (D == 64);
   static_assert(kColO + 2 * D <= kTmemCols, "TMEM budget");
 
   extern __shared__ uint8_t smem_dyn[];
@@ -202,6 +231,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     for (int i = 0; i < kSBufs; ++i) {
       mbar_init(bar(L::kSFull + i), 1);
       mbar_init(bar(L::kPFull + i), 8);  // one arrival per sigmoid warp of the query tile
+      mbar_init(bar(L::kPvDone + i), 1);
     }
     mbar_init(bar(L::kOFull), 1);
     mbar_init(bar(L::kVFix), 1);
@@ -283,7 +313,45 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       }
     }
   } else if (warp == kFwdIssuerWarp) {
-    // ============================================================ tcgen05 issuer
+    if constexpr (kSplitIssue) {
+    // ============================================================ tcgen05 issuer 1: S = Q K^T
+    // Two issuing warps (this one for the scores, the next for P V): an issuing warp's
+    // instruction stream is one long dependent chain (waits, MMAs, commits), and a single warp
+    // doing both products was what bounded the kernel.  All ring positions, stage numbers and
+    // barrier parities are carried incrementally (no division, no modulo), and descriptors are a
+    // precomputed base plus a constant in the start-address field.
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_qk = make_idesc(128, 128, kBF16, false, false);
+    constexpr uint32_t kStageStep = kTileBytes >> 4;  // one smem stage, in descriptor address units
+    const int n_jobs = n0 + n1;
+    // Q tile 0 and K stage 0: rows = M/N, the 64 contiguous elements = contraction
+    const uint64_t q_desc0 = smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
+    const uint64_t k_desc0 = smem_desc_sw128(smem_base + L::kKOff, 16, 1024);
+    const uint32_t q_lo = (uint32_t)q_desc0, k_lo = (uint32_t)k_desc0, hi = (uint32_t)(q_desc0 >> 32);
+    FwdCursor c{(n0 > 0) ? 0 : 1, 0, 0, 0u, 0, 0u, true};
+    bool ok = true;
+    for (int n = 0; n < n_jobs && ok; ++n) {
+      if (c.j == 0) ok = mbar_wait_warp(bar(L::kQFull + c.s), 0, abort_flag, kSiteBase + 3);
+      if (c.fresh) ok = ok && mbar_wait_warp(bar(L::kKFull + c.st), c.ph, abort_flag, kSiteBase + 5);
+      // the buffer still holds the probabilities of job n - kSBufs until their P V product is complete
+      if (n >= kSBufs) ok = ok && mbar_wait_warp(bar(L::kPvDone + c.buf), c.bph ^ 1u, abort_flag, kSiteBase + 4);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t qa = q_lo + (uint32_t)c.s * kStageStep;
+      const uint32_t ka = k_lo + (uint32_t)c.st * kStageStep;
+      const uint32_t dst = tmem + kColS + 128u * (uint32_t)c.buf;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = (uint32_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+        mma_ss(leader, dst, make_desc(qa + off, hi), make_desc(ka + off, hi), idesc_qk, kk > 0);
+      }
+      mma_commit(leader, bar(L::kSFull + c.buf));
+      // last job that reads K_j: hand the stage back to the producer
+      if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kKEmpty + c.st));
+      c.advance(n0, n1, kStages, kSBufs);
+    }
+    } else {
+    // ============================================================ single tcgen05 issuer (D = 128)
     // This warp's instruction stream is one long dependent chain, so its length per job decides
     // how quickly finished probabilities turn into new scores: all ring positions, stage numbers
     // and barrier parities are carried incrementally (no division, no modulo), and descriptors
@@ -304,44 +372,16 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const uint32_t k_lo = (uint32_t)k_desc0, k_hi = (uint32_t)(k_desc0 >> 32);
       const uint32_t v_lo = (uint32_t)v_desc0, v_hi = (uint32_t)(v_desc0 >> 32);
 
-      // Cursor over the job order (0,0) (1,0) (0,1) (1,1) ... restricted to j < n_kv[s].
-      struct Cursor {
-        int s, j;         // query tile, key tile
-        int st;           // smem stage of key tile j
-        uint32_t ph;      // parity of that stage's "full" barrier
-        int buf;          // S buffer of the job
-        uint32_t bph;     // parity of that buffer's barriers
-        bool fresh;       // first job that touches key tile j
-      };
-      auto advance = [&](Cursor& c) {
-        if (c.s == 0 && c.j < n1) {
-          c.s = 1;
-          c.fresh = false;
-        } else {
-          ++c.j;
-          c.s = (c.j < n0) ? 0 : 1;
-          if (++c.st == kStages) { c.st = 0; c.ph ^= 1u; }
-          c.fresh = true;
-        }
-        if (++c.buf == kSBufs) { c.buf = 0; c.bph ^= 1u; }
-      };
-      Cursor cs{(n0 > 0) ? 0 : 1, 0, 0, 0u, 0, 0u, true};  // next scores to issue
-      Cursor cp = cs;                                      // next P V product to issue
+      FwdCursor cs{(n0 > 0) ? 0 : 1, 0, 0, 0u, 0, 0u, true};  // next scores to issue
+      FwdCursor cp = cs;                                      // next P V product to issue
 
-#ifdef SIG_TRACE
-      long long tr_wait = 0, tr_mma = 0;
-      const long long tr_begin = clock64();
-#endif
       // S[buf] = Q_s K_j^T
-      auto issue_s = [&](const Cursor& c) {
+      auto issue_s = [&](const FwdCursor& c) {
         {
-          SIG_T0();
           if (c.j == 0) ok = ok && mbar_wait_warp(bar(L::kQFull + c.s), 0, abort_flag, kSiteBase + 3);
           if (c.fresh) ok = ok && mbar_wait_warp(bar(L::kKFull + c.st), c.ph, abort_flag, kSiteBase + 5);
-          SIG_TACC(tr_wait);
         }
         if (!ok) return;
-        SIG_T0();
         const uint32_t qa = q_lo + (uint32_t)c.s * kStageStep;
         const uint32_t ka = k_lo + (uint32_t)c.st * kStageStep;
         const uint32_t dst = tmem + kColS + 128u * (uint32_t)c.buf;
@@ -353,22 +393,18 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         mma_commit(leader, bar(L::kSFull + c.buf));
         // last job that reads K_j: hand the stage back to the producer
         if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kKEmpty + c.st));
-        SIG_TACC(tr_mma);
       };
       // O_s += P[buf] V_j
-      auto issue_pv = [&](const Cursor& c) {
+      auto issue_pv = [&](const FwdCursor& c) {
         {
-          SIG_T0();
           if (c.fresh) {
             ok = ok && mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
             if (c.j * kTileN + kTileN > Lk)  // padded V rows are being cleared by the producer warp
               ok = ok && mbar_wait_warp(bar(L::kVFix), 0, abort_flag, kSiteBase + 14);
           }
           ok = ok && mbar_wait_warp(bar(L::kPFull + c.buf), c.bph, abort_flag, kSiteBase + 7);
-          SIG_TACC(tr_wait);
         }
         if (!ok) return;
-        SIG_T0();
         tc_fence_after_sync();
         const uint32_t va = v_lo + (uint32_t)c.st * kStageStep;
         const uint32_t pa = tmem + kColS + 128u * (uint32_t)c.buf;
@@ -381,30 +417,64 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
                  kk > 0 ? 1u : acc0);
         }
         if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
-        SIG_TACC(tr_mma);
       };
 
       int n_s = 0;
       for (; n_s < kSBufs && n_s < n_jobs && ok; ++n_s) {
         issue_s(cs);
-        advance(cs);
+        cs.advance(n0, n1, kStages, kSBufs);
       }
       for (int n = 0; n < n_jobs && ok; ++n) {
         issue_pv(cp);
-        advance(cp);
+        cp.advance(n0, n1, kStages, kSBufs);
         if (n_s < n_jobs && ok) {
           issue_s(cs);  // reuses the buffer the product above has just consumed
-          advance(cs);
+          cs.advance(n0, n1, kStages, kSBufs);
           ++n_s;
         }
       }
       if (ok) mma_commit(leader, bar(L::kOFull));
-#ifdef SIG_TRACE
-      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) {
-        g_trace[32] = tr_wait; g_trace[33] = clock64() - tr_begin; g_trace[34] = n_jobs; g_trace[35] = tr_mma;
-      }
-#endif
     }
+    }
+  } else if (warp == kFwdIssuerWarp2) {
+    if constexpr (kSplitIssue) {
+    // ============================================================ tcgen05 issuer 2: O_s += P V_j
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_pv = make_idesc(128, D, kBF16, false, true);
+    constexpr uint32_t kStageStep = kTileBytes >> 4;
+    const int n_jobs = n0 + n1;
+    // V stage 0: rows = contraction, the 64 contiguous elements = N, next 64-column block 16 KB further
+    const uint64_t v_desc0 = smem_desc_sw128(smem_base + L::kVOff, 16384, 1024);
+    const uint32_t v_lo = (uint32_t)v_desc0, hi = (uint32_t)(v_desc0 >> 32);
+    FwdCursor c{(n0 > 0) ? 0 : 1, 0, 0, 0u, 0, 0u, true};
+    bool ok = true;
+    for (int n = 0; n < n_jobs && ok; ++n) {
+      if (c.fresh) {
+        ok = mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
+        if (c.j * kTileN + kTileN > Lk)  // padded V rows are being cleared by the producer warp
+          ok = ok && mbar_wait_warp(bar(L::kVFix), 0, abort_flag, kSiteBase + 14);
+      }
+      ok = ok && mbar_wait_warp(bar(L::kPFull + c.buf), c.bph, abort_flag, kSiteBase + 7);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t va = v_lo + (uint32_t)c.st * kStageStep;
+      const uint32_t pa = tmem + kColS + 128u * (uint32_t)c.buf;
+      const uint32_t dst = tmem + kColO + (uint32_t)(D * c.s);
+      const uint32_t acc0 = c.j > 0 ? 1u : 0u;
+#pragma unroll
+      for (int kk = 0; kk < kTileN / 16; ++kk) {
+        // P of key columns [64g, 64g+64) sits, 16-bit packed, in buffer columns 64g + [0,32)
+        mma_ts(leader, dst, pa + 64 * (kk >> 2) + 8 * (kk & 3), make_desc(va + kk * (2048 >> 4), hi), idesc_pv,
+               kk > 0 ? 1u : acc0);
+      }
+      mma_commit(leader, bar(L::kPvDone + c.buf));
+      if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
+      c.advance(n0, n1, kStages, kSBufs);
+    }
+    if (ok) mma_commit(leader, bar(L::kOFull));
+    }
+  } else if (warp >= kFwdSigmoidWarps) {
+    // idle warp
   } else {
     // ============================================================ sigmoid groups + epilogue
     const int s = warp >> 3;                              // query tile
