@@ -111,19 +111,33 @@ __device__ __forceinline__ void bwd_phase_a(uint32_t s_addr, float c1, float c0,
   uint32_t r[32];
   tmem_ld32_sync(s_addr, r);
   uint32_t pk[16];
+  float2 t[16];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float2 t = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])),
-                                make_float2(c1, c1), make_float2(c0, c0));
-    float2 pe = sigmoid2_from_log2<kBF16>(t);
-    if constexpr (kMask) {
-      const int q = q0 + 2 * i;
-      pe.x = (q >= q_lo && q < q_hi) ? pe.x : 0.0f;
-      pe.y = (q + 1 >= q_lo && q + 1 < q_hi) ? pe.y : 0.0f;
+  for (int i = 0; i < 16; ++i)
+    t[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), make_float2(c1, c1),
+                      make_float2(c0, c0));
+  // all logits negative (the usual case under the default bias): no compare / select per element
+  if (!kMask && warp_all_negative(t)) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float2 pe = sigmoid2_from_log2_neg<kBF16>(t[i]);
+      pv[2 * i] = pe.x;
+      pv[2 * i + 1] = pe.y;
+      pk[i] = pack2<kBF16>(pe.x, pe.y);
     }
-    pv[2 * i] = pe.x;
-    pv[2 * i + 1] = pe.y;
-    pk[i] = pack2<kBF16>(pe.x, pe.y);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float2 pe = sigmoid2_from_log2<kBF16>(t[i]);
+      if constexpr (kMask) {
+        const int q = q0 + 2 * i;
+        pe.x = (q >= q_lo && q < q_hi) ? pe.x : 0.0f;
+        pe.y = (q + 1 >= q_lo && q + 1 < q_hi) ? pe.y : 0.0f;
+      }
+      pv[2 * i] = pe.x;
+      pv[2 * i + 1] = pe.y;
+      pk[i] = pack2<kBF16>(pe.x, pe.y);
+    }
   }
   tmem_st16(s_addr, pk);
 }
@@ -456,7 +470,6 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kDqEmpty));  // the TMEM columns are free again
-#ifndef SIG_EXP_NORED
         const int q_first = q_tile + 32 * cg;
         float* dst = p.dq_acc + (((int64_t)b * p.Tq + q_first) * p.H + h) * D + lane_row;
         const int64_t row_stride = (int64_t)p.H * D;
@@ -466,7 +479,6 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           if (v < n_live)
             asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + v * row_stride), "f"(__uint_as_float(r[v])) : "memory");
         }
-#endif
       } else {
         uint32_t r[16];
         tmem_ld16(dq_addr, r);
@@ -474,7 +486,6 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kDqEmpty));
-#ifndef SIG_EXP_NORED
         const int q = q_tile + lane_row;
         if (q < Lq) {  // queries at or beyond Lq get no gradient
           float* dst = p.dq_acc + (((int64_t)b * p.Tq + q) * p.H + h) * D + 16 * cg;
@@ -486,7 +497,6 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
                          : "memory");
           }
         }
-#endif
       }
     };
 
@@ -501,9 +511,6 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       ok = mbar_wait_warp(bar(L::kSFull), (uint32_t)t & 1u, abort_flag, kSiteBase + 12);
       if (!ok) break;
       tc_fence_after_sync();
-#ifdef SIG_EXP_BWD_NOCOMPUTE
-      if (p.Tq < 0)
-#endif
       if (need_mask) bwd_phase_a<kBF16, true>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
       else           bwd_phase_a<kBF16, false>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
       tmem_st_wait();
@@ -521,9 +528,6 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       ok = mbar_wait_warp(bar(L::kDpFull), (uint32_t)t & 1u, abort_flag, kSiteBase + 13);
       if (!ok) break;
       tc_fence_after_sync();
-#ifdef SIG_EXP_BWD_NOCOMPUTE
-      if (p.Tq < 0)
-#endif
       if (need_mask) bwd_phase_b<kBF16, true>(dp_addr, ds_line, chunk0, sw, pv);
       else           bwd_phase_b<kBF16, false>(dp_addr, ds_line, chunk0, sw, pv);
       fence_proxy_async_smem();

@@ -42,17 +42,8 @@ struct FwdParams {
   int n_qblk;  // ceil(Tq / 256)
 };
 
-#ifdef SIG_TRACE
-// experiment-only cycle counters of block (0,0,0): [role][counter]
-__device__ long long g_trace[64];
-#define SIG_T0() const long long t0_ = clock64()
-#define SIG_TACC(var) var += clock64() - t0_
-#else
-#define SIG_T0()
-#define SIG_TACC(var)
-#endif
 #ifndef SIG_FWD_CHUNK
-#define SIG_FWD_CHUNK 32
+#define SIG_FWD_CHUNK 32  // score columns per TMEM load of a sigmoid thread (32 measured faster than 16)
 #endif
 constexpr int kFwdSigmoidWarps = 16;
 constexpr int kFwdProducerWarp = 16;
@@ -128,21 +119,36 @@ __device__ __forceinline__ void fwd_sigmoid_half_tile(uint32_t s_addr, float c1,
     tmem_ld_wait_for(r);
     if (c + 1 < kNCh) tmem_ld(s_addr + (c + 1) * kCh, rbuf[(c + 1) & 1]);
     uint32_t pk[kCh / 2];
+    float2 t[kCh / 2];
 #pragma unroll
     for (int i = 0; i < kCh / 2; ++i) {
-      float2 t = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])),
-                            make_float2(c1, c1), make_float2(c0, c0));
-      const int col = col0 + c * kCh + 2 * i;
+      t[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), make_float2(c1, c1),
+                        make_float2(c0, c0));
       if constexpr (kScoreMod) {
-        t.x = fmaf(col < Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t.x);
-        t.y = fmaf(col + 1 < Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t.y);
+        const int col = col0 + c * kCh + 2 * i;
+        t[i].x = fmaf(col < Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t[i].x);
+        t[i].y = fmaf(col + 1 < Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t[i].y);
       }
-      float2 pr = sigmoid2_from_log2<kBF16>(t);
-      if constexpr (kMask) {
-        pr.x = (col <= lim) ? pr.x : 0.0f;
-        pr.y = (col + 1 <= lim) ? pr.y : 0.0f;
+    }
+    // Under the default bias every logit of a chunk is negative: then the sign handling (one
+    // compare and one select per element) is skipped for the whole warp.
+    if (!kMask && warp_all_negative(t)) {
+#pragma unroll
+      for (int i = 0; i < kCh / 2; ++i) {
+        const float2 pr = sigmoid2_from_log2_neg<kBF16>(t[i]);
+        pk[i] = pack2<kBF16>(pr.x, pr.y);
       }
-      pk[i] = pack2<kBF16>(pr.x, pr.y);
+    } else {
+#pragma unroll
+      for (int i = 0; i < kCh / 2; ++i) {
+        float2 pr = sigmoid2_from_log2<kBF16>(t[i]);
+        if constexpr (kMask) {
+          const int col = col0 + c * kCh + 2 * i;
+          pr.x = (col <= lim) ? pr.x : 0.0f;
+          pr.y = (col + 1 <= lim) ? pr.y : 0.0f;
+        }
+        pk[i] = pack2<kBF16>(pr.x, pr.y);
+      }
     }
     tmem_st(s_addr + c * (kCh / 2), pk);
   }
@@ -271,9 +277,6 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const uint32_t ph = (j / kStages) & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kKEmpty + st), ph ^ 1, abort_flag, kSiteBase + 1));
       if (!ok) break;
-#ifdef SIG_EXP_NOLOAD
-      if (lane == 0 && j >= kStages) mbar_arrive(bar(L::kKFull + st)); else
-#endif
       if (lane == 0) {
         mbar_expect_tx(bar(L::kKFull + st), kTileBytes);
 #pragma unroll
@@ -283,9 +286,6 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       }
       ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kVEmpty + st), ph ^ 1, abort_flag, kSiteBase + 2));
       if (!ok) break;
-#ifdef SIG_EXP_NOLOAD
-      if (lane == 0 && j >= kStages) mbar_arrive(bar(L::kVFull + st)); else
-#endif
       if (lane == 0) {
         mbar_expect_tx(bar(L::kVFull + st), kTileBytes);
 #pragma unroll
@@ -491,18 +491,12 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     int lim = Lk - 1;
     if (p.causal) lim = min(lim, row);
     bool ok = true;
-#ifdef SIG_TRACE
-    long long tr_wait = 0, tr_comp = 0, tr_tail = 0;
-    const long long tr_begin = clock64();
-#endif
 
     for (int j = 0; j < n_mine; ++j) {
       const int n = job_index(s, j);
       const int buf = n % kSBufs;
       {
-        SIG_T0();
         ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull + buf), (n / kSBufs) & 1, abort_flag, kSiteBase + 10 + s));
-        SIG_TACC(tr_wait);
       }
       if (!ok) break;
       tc_fence_after_sync();
@@ -511,32 +505,19 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const bool need_mask = (col0 + 64 > Lk) || (p.causal && col0 + 63 > q0 + 128 * s);
       // the predicate code exists only in the instantiation used by boundary tiles
       {
-        SIG_T0();
-#ifdef SIG_EXP_NOSIGMOID
-        if (p.Tq < 0)
-#endif
         if (need_mask)
           fwd_sigmoid_half_tile<kBF16, kScoreMod, true>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
         else
           fwd_sigmoid_half_tile<kBF16, kScoreMod, false>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
-        SIG_TACC(tr_comp);
       }
       {
-        SIG_T0();
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kPFull + buf));  // 256 arrivals on one barrier would serialise
-        SIG_TACC(tr_tail);
       }
     }
 
-#ifdef SIG_TRACE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0) {
-      long long* tr = g_trace + (warp >> 2) * 4;
-      tr[0] = tr_wait; tr[1] = tr_comp; tr[2] = tr_tail; tr[3] = clock64() - tr_begin;
-    }
-#endif
     if (n_mine == 0) {
       // this tile is entirely padding (or beyond Tq): zero rows
       if (row < p.Tq) {

@@ -268,13 +268,6 @@ int sigattn_device_status(int device) {
   return v;
 }
 
-#ifdef SIG_TRACE
-// experiment builds only: copy the cycle counters of the forward kernel's block (0,0,0)
-int sigattn_debug_trace(long long* out, int n) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, sigattn::g_trace, sizeof(long long) * (n < 64 ? n : 64));
-}
-#endif
 
 int sigattn_fwd(const SigAttnParams* p) {
   g_err[0] = 0;
