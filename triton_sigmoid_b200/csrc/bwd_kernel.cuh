@@ -21,10 +21,10 @@
 //                                  red.global.add.f32 per query covers a full 128-byte line;
 //                                D = 64: M = 64 would idle half of the tensor core and half of
 //                                  the lanes, and staging rows in shared memory for bulk
-//                                  reductions measured slower than the plain form, so each
-//                                  thread adds its 64 bytes of a row with four
-//                                  red.global.add.v4.f32 (the reduction traffic, not the math,
-//                                  is what bounds this case).
+//                                  the lanes, so each warp regroups its 32 rows x 64 bytes through
+//                                  a private shared-memory patch and adds them with
+//                                  red.global.add.v4.f32, four lanes per 64-byte run (the
+//                                  reduction traffic, not the math, is what bounds this case).
 //
 // Warp roles (20 warps):
 //   warps 0-15  compute: warp w owns TMEM lanes (key rows) 32 (w & 3) .. +31 and the query
@@ -79,21 +79,26 @@ struct BwdSmem {
   static constexpr int kDoOff = kQOff + kStages * kTileBytes;
   static constexpr int kDsOff = kDoOff + kStages * kTileBytes;
   static constexpr int kDsBytes = 128 * 128 * 2;
-  static constexpr int kBarOff = kDsOff + kDsBytes;
+  // D = 64 only: a private 32-row x 80-byte patch per compute warp, used to regroup dQ rows so that
+  // four adjacent lanes add 64 consecutive bytes (80 = 64 + 16 keeps the 16-byte accesses off each
+  // other's banks)
+  static constexpr int kDqPatchOff = kDsOff + kDsBytes;
+  static constexpr int kDqPatchBytes = (D == 64) ? 32 * 80 : 0;
+  static constexpr int kBarOff = kDqPatchOff + 16 * kDqPatchBytes;
   static constexpr int kKvFull = 0;
   static constexpr int kQFull = 1;                    // [2]
   static constexpr int kQEmpty = kQFull + kStages;    // [2]  both issuers release a stage
   static constexpr int kDoFull = kQEmpty + kStages;   // [2]
   static constexpr int kDoEmpty = kDoFull + kStages;  // [2]
-  static constexpr int kSFull = kDoEmpty + kStages;   // S^T written
-  static constexpr int kDpFull = kSFull + 1;          // dP^T written
-  static constexpr int kPReady = kDpFull + 1;         // P^T in TMEM (16 warps)
-  static constexpr int kDsReady = kPReady + 1;        // dS^T in TMEM and shared memory (16 warps)
+  static constexpr int kSFull = kDoEmpty + kStages;   // [2] S^T written (per S buffer)
+  static constexpr int kDpFull = kSFull + 2;          // dP^T written
+  static constexpr int kPReady = kDpFull + 1;         // [2] P^T in TMEM (16 warps; per S buffer)
+  static constexpr int kDsReady = kPReady + 2;        // dS^T in TMEM and shared memory (16 warps)
   static constexpr int kSFree = kDsReady + 1;         // dV has consumed P^T: S columns reusable
   static constexpr int kDpFree = kSFree + 1;          // dK has consumed dS^T: dP columns reusable
-  static constexpr int kDqFull = kDpFree + 1;         // dQ tile complete in TMEM
-  static constexpr int kDqEmpty = kDqFull + 1;        // dQ tile read out (16 warps)
-  static constexpr int kDkvFull = kDqEmpty + 1;       // every MMA of the CTA complete
+  static constexpr int kDqFull = kDpFree + 1;         // [2] dQ tile complete in TMEM
+  static constexpr int kDqEmpty = kDqFull + 2;        // [2] dQ tile read out (16 warps)
+  static constexpr int kDkvFull = kDqEmpty + 2;       // every MMA of the CTA complete
   static constexpr int kKvFix = kDkvFull + 1;         // padded rows of K_j zeroed
   static constexpr int kQdoFix = kKvFix + 1;          // padded rows of the last Q_i / dO_i zeroed
   static constexpr int kNumBars = kQdoFix + 1;
@@ -179,13 +184,23 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   using L = BwdSmem<D>;
   constexpr int kTileBytes = L::kTileBytes;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0;             // S^T (128 fp32 columns); column group c keeps P^T in 32c + [0,16)
-  constexpr uint32_t kColDp = 128;          // dP^T; column group c keeps dS^T in 32c + [0,16)
-  constexpr uint32_t kColDv = 256;
-  constexpr uint32_t kColDk = 256 + D;
+  // TMEM plan.  D = 64: two S^T buffers (tiles alternate), so that the scores of the next tile are
+  // computed while this one is still being processed; dQ_i is written over the S^T buffer of its
+  // own tile once dV has read P^T from it:   S0 0 | S1 128 | dP 256 | dV 384 | dK 448.
+  // D = 128: no room for that: one S^T buffer, dQ^T over the dP^T columns:  S 0 | dP 128 | dV 256 | dK 384.
+  // Column group c keeps its 16-bit P^T in S columns 32c + [0,16), dS^T likewise in the dP columns.
+  constexpr bool kTwoS = (D == 64);
   constexpr bool kDqT = (D == 128);         // dQ^T (head dimension on lanes) instead of dQ
-  constexpr bool kDqAliased = (D == 128);   // no room left: dQ^T reuses the dP^T columns
-  constexpr uint32_t kColDq = kDqAliased ? kColDp : 384;
+  constexpr uint32_t kColS = 0;
+  constexpr uint32_t kColDp = kTwoS ? 256 : 128;
+  constexpr uint32_t kColDv = kTwoS ? 384 : 256;
+  constexpr uint32_t kColDk = kColDv + D;
+  static_assert(kColDk + D <= kTmemCols, "TMEM budget");
+  // index and parity of the per-S-buffer barriers for tile t
+  auto sbuf = [](int t) -> int { return kTwoS ? (t & 1) : 0; };
+  auto spar = [](int t) -> uint32_t { return kTwoS ? (uint32_t)(t >> 1) & 1u : (uint32_t)t & 1u; };
+  // where dQ (or dQ^T) of tile t is written
+  auto dq_col = [&](int t) -> uint32_t { return kTwoS ? kColS + 128u * (uint32_t)(t & 1) : kColDp; };
   constexpr int kSiteBase = 0x20000;
 
   extern __shared__ uint8_t smem_dyn[];
@@ -242,14 +257,18 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       mbar_init(bar(L::kDoFull + i), 1);
       mbar_init(bar(L::kDoEmpty + i), 2);  // dP^T (issuer A) and dV (issuer B) both read dO_i
     }
-    mbar_init(bar(L::kSFull), 1);
+    mbar_init(bar(L::kSFull + 0), 1);
+    mbar_init(bar(L::kSFull + 1), 1);
     mbar_init(bar(L::kDpFull), 1);
-    mbar_init(bar(L::kPReady), kBwdComputeWarps);
+    mbar_init(bar(L::kPReady + 0), kBwdComputeWarps);
+    mbar_init(bar(L::kPReady + 1), kBwdComputeWarps);
     mbar_init(bar(L::kDsReady), kBwdComputeWarps);
     mbar_init(bar(L::kSFree), 1);
     mbar_init(bar(L::kDpFree), 1);
-    mbar_init(bar(L::kDqFull), 1);
-    mbar_init(bar(L::kDqEmpty), kBwdComputeWarps);
+    mbar_init(bar(L::kDqFull + 0), 1);
+    mbar_init(bar(L::kDqFull + 1), 1);
+    mbar_init(bar(L::kDqEmpty + 0), kBwdComputeWarps);
+    mbar_init(bar(L::kDqEmpty + 1), kBwdComputeWarps);
     mbar_init(bar(L::kDkvFull), 1);
     mbar_init(bar(L::kKvFix), 1);
     mbar_init(bar(L::kQdoFix), 1);
@@ -359,18 +378,23 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const uint32_t prev = (uint32_t)(t - 1) & 1u;
       ok = mbar_wait_warp(bar(L::kQFull + st), ph, abort_flag, kSiteBase + 4);
       if (t == n_q - 1 && ragged_last_q) ok = ok && mbar_wait_warp(bar(L::kQdoFix), 0, abort_flag, kSiteBase + 21);
-      // the S columns still hold P^T of the previous tile until its dV GEMM has read them
-      if (t > 0) ok = ok && mbar_wait_warp(bar(L::kSFree), prev, abort_flag, kSiteBase + 5);
+      if constexpr (kTwoS) {
+        // this S buffer last held tile t-2: its P^T (read by dV) and then its dQ, until that was drained
+        if (t >= 2) ok = ok && mbar_wait_warp(bar(L::kDqEmpty + sbuf(t)), spar(t - 2), abort_flag, kSiteBase + 5);
+      } else {
+        // the S columns still hold P^T of the previous tile until its dV GEMM has read them
+        if (t > 0) ok = ok && mbar_wait_warp(bar(L::kSFree), prev, abort_flag, kSiteBase + 5);
+      }
       if (!ok) break;
       tc_fence_after_sync();
-      issue(kColS, k_lo, q_lo0 + (uint32_t)st * kStageStep);
-      mma_commit(leader, bar(L::kSFull));
+      issue(kColS + 128u * (uint32_t)sbuf(t), k_lo, q_lo0 + (uint32_t)st * kStageStep);
+      mma_commit(leader, bar(L::kSFull + sbuf(t)));
       mma_commit(leader, bar(L::kQEmpty + st));
       ok = mbar_wait_warp(bar(L::kDoFull + st), ph, abort_flag, kSiteBase + 6);
       if (t > 0) {
         // the dP columns hold dS^T of the previous tile (read by dK) and, when dQ shares them,
         // the previous dQ tile until it has been drained
-        ok = ok && mbar_wait_warp(bar(kDqAliased ? L::kDqEmpty : L::kDpFree), prev, abort_flag, kSiteBase + 7);
+        ok = ok && mbar_wait_warp(bar(kDqT ? L::kDqEmpty : L::kDpFree), prev, abort_flag, kSiteBase + 7);
       }
       if (!ok) break;
       tc_fence_after_sync();
@@ -409,29 +433,33 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const uint32_t par = (uint32_t)t & 1u;
       const uint32_t acc0 = t > 0 ? 1u : 0u;
       // dV += P^T dO
-      ok = mbar_wait_warp(bar(L::kPReady), par, abort_flag, kSiteBase + 8);
+      ok = mbar_wait_warp(bar(L::kPReady + sbuf(t)), spar(t), abort_flag, kSiteBase + 8);
       if (!ok) break;
       tc_fence_after_sync();
-      issue_acc(kColDv, kColS, do_lo0 + (uint32_t)st * kStageStep, acc0);
-      mma_commit(leader, bar(L::kSFree));
+      issue_acc(kColDv, kColS + 128u * (uint32_t)sbuf(t), do_lo0 + (uint32_t)st * kStageStep, acc0);
+      if (!kTwoS) mma_commit(leader, bar(L::kSFree));
       mma_commit(leader, bar(L::kDoEmpty + st));
       // dK += dS^T Q
       ok = mbar_wait_warp(bar(L::kDsReady), par, abort_flag, kSiteBase + 9);
       if (!ok) break;
       tc_fence_after_sync();
       issue_acc(kColDk, kColDp, q_lo0 + (uint32_t)st * kStageStep, acc0);
-      if (!kDqAliased) mma_commit(leader, bar(L::kDpFree));
+      if (!kDqT) mma_commit(leader, bar(L::kDpFree));
       mma_commit(leader, bar(L::kQEmpty + st));
       // the dQ GEMM needs the previous dQ tile read out of its columns
-      ok = mbar_wait_warp(bar(L::kDqEmpty), par ^ 1u, abort_flag, kSiteBase + 10);
-      if (!ok) break;
-      tc_fence_after_sync();
+      if constexpr (!kTwoS) {
+        ok = mbar_wait_warp(bar(L::kDqEmpty), par ^ 1u, abort_flag, kSiteBase + 10);
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      // (two S buffers: dQ goes over this tile's own S^T buffer; dV above, issued by this same
+      //  thread and therefore executed earlier, was the last reader of P^T in it)
 #pragma unroll
       for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
         const uint64_t kd = make_desc(k_lo + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
-        mma_ss(leader, tmem + kColDq, kDqT ? kd : dsd, kDqT ? dsd : kd, idesc_dq, kk > 0);
+        mma_ss(leader, tmem + dq_col(t), kDqT ? kd : dsd, kDqT ? dsd : kd, idesc_dq, kk > 0);
       }
-      mma_commit(leader, bar(L::kDqFull));
+      mma_commit(leader, bar(L::kDqFull + sbuf(t)));
       st ^= 1;
     }
     if (ok) mma_commit(leader, bar(L::kDkvFull));
@@ -442,7 +470,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     const int lane_row = quarter * 32 + lane;             // key row within the tile == TMEM lane
     const int kv = kv0 + lane_row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_addr = tmem + lane_addr + kColS + 32 * cg;
+    const uint32_t s_addr0 = tmem + lane_addr + kColS + 32 * cg;  // + 128 for the second S buffer
     const uint32_t dp_addr = tmem + lane_addr + kColDp + 32 * cg;
     const float c1 = p.scale * kLog2e;
     float c0 = p.bias ? p.bias[b] : p.bias_scalar;
@@ -458,9 +486,10 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     // ---- dQ drain (see the file header)
     // D = 128: lane l of quarter k holds d = 32 k + l of dQ^T; this warp takes query columns 32 cg ..
     // D = 64:  this thread holds query row `lane_row`, head columns 16 cg .. 16 cg + 15 of dQ
-    const uint32_t dq_addr = tmem + lane_addr + kColDq + (kDqT ? 32 : 16) * cg;
+    const uint32_t dq_off = tmem + lane_addr + (kDqT ? 32 : 16) * cg;
     auto drain_dq = [&](int t) {  // t = local index of the query tile whose dQ is complete
-      ok = mbar_wait_warp(bar(L::kDqFull), (uint32_t)t & 1u, abort_flag, kSiteBase + 14);
+      ok = mbar_wait_warp(bar(L::kDqFull + sbuf(t)), spar(t), abort_flag, kSiteBase + 14);
+      const uint32_t dq_addr = dq_off + dq_col(t);
       if (!ok) return;
       tc_fence_after_sync();
       const int q_tile = (i_begin + t) * kBwdTileQ;
@@ -469,7 +498,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         tmem_ld32_sync(dq_addr, r);
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kDqEmpty));  // the TMEM columns are free again
+        if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(t)));  // the TMEM columns are free again
         const int q_first = q_tile + 32 * cg;
         float* dst = p.dq_acc + (((int64_t)b * p.Tq + q_first) * p.H + h) * D + lane_row;
         const int64_t row_stride = (int64_t)p.H * D;
@@ -485,18 +514,31 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         tmem_ld_wait_for(r);
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kDqEmpty));
-        const int q = q_tile + lane_row;
-        if (q < Lq) {  // queries at or beyond Lq get no gradient
-          float* dst = p.dq_acc + (((int64_t)b * p.Tq + q) * p.H + h) * D + 16 * cg;
+        if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(t)));
+        // Lane l holds 64 bytes of row l.  Adding them as they are would make every reduction
+        // instruction touch 32 rows with 16 bytes each, and the L2 handles such half-sector requests
+        // at half its rate.  Through the warp's shared-memory patch the data is regrouped so that lane
+        // l holds bytes 16 (l & 3) .. +15 of rows 8 k + (l >> 2), k = 0..3: four lanes per 64-byte run.
+        // (Bulk reductions out of shared memory, per row or per 256-byte row across warps, measured
+        // slower than this: they compete with the tile loads for the copy engine.)
+        uint8_t* patch = smem_gen + L::kDqPatchOff + warp * L::kDqPatchBytes;
+        uint4* mine = reinterpret_cast<uint4*>(patch + lane * 80);
 #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + v4 * 4),
-                         "f"(__uint_as_float(r[4 * v4])), "f"(__uint_as_float(r[4 * v4 + 1])),
-                         "f"(__uint_as_float(r[4 * v4 + 2])), "f"(__uint_as_float(r[4 * v4 + 3]))
+        for (int m = 0; m < 4; ++m) mine[m] = make_uint4(r[4 * m], r[4 * m + 1], r[4 * m + 2], r[4 * m + 3]);
+        __syncwarp();
+        const int sub_row = lane >> 2, chunk = lane & 3;
+        float* dst = p.dq_acc + (((int64_t)b * p.Tq + q_tile + quarter * 32 + sub_row) * p.H + h) * D + 16 * cg + 4 * chunk;
+        const int64_t step = (int64_t)8 * p.H * D;  // eight rows further
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint4 w = *reinterpret_cast<const uint4*>(patch + (8 * k + sub_row) * 80 + chunk * 16);
+          if (q_tile + quarter * 32 + 8 * k + sub_row < Lq) {  // queries at or beyond Lq get no gradient
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + k * step), "f"(__uint_as_float(w.x)),
+                         "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
                          : "memory");
           }
         }
+        __syncwarp();  // the patch is rewritten at the next tile
       }
     };
 
@@ -508,7 +550,8 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       // warp-uniform on purpose: the two instantiations contain warp-collective TMEM accesses
       const bool need_mask = ragged_kv || (q0 + 32 > Lq) || (p.causal && q0 < kv0 + kBwdTileKV - 1);
       float pv[32];
-      ok = mbar_wait_warp(bar(L::kSFull), (uint32_t)t & 1u, abort_flag, kSiteBase + 12);
+      ok = mbar_wait_warp(bar(L::kSFull + sbuf(t)), spar(t), abort_flag, kSiteBase + 12);
+      const uint32_t s_addr = s_addr0 + 128u * (uint32_t)sbuf(t);
       if (!ok) break;
       tc_fence_after_sync();
       if (need_mask) bwd_phase_a<kBF16, true>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
@@ -516,7 +559,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(L::kPReady));
+      if (lane == 0) mbar_arrive(bar(L::kPReady + sbuf(t)));
 
       // dQ of the previous tile is complete by now (or soon): drain it while dP^T is computed.
       // Its completion also means the dQ GEMM no longer reads the shared-memory copy of dS.
