@@ -124,10 +124,24 @@ __device__ __forceinline__ void fwd_sigmoid_half_tile(uint32_t s_addr, float c1,
     for (int i = 0; i < kCh / 2; ++i) {
       t[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), make_float2(c1, c1),
                         make_float2(c0, c0));
-      if constexpr (kScoreMod) {
-        const int col = col0 + c * kCh + 2 * i;
-        t[i].x = fmaf(col < Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t[i].x);
-        t[i].y = fmaf(col + 1 < Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t[i].y);
+    }
+    if constexpr (kScoreMod) {
+      // per-key additive bias: the same value for every lane (row), read through the read-only path
+      const int cbase = col0 + c * kCh;
+      if (cbase + kCh <= Tk && (reinterpret_cast<uintptr_t>(sm_row + cbase) & 15u) == 0) {
+#pragma unroll
+        for (int i = 0; i < kCh / 4; ++i) {
+          const float4 m = __ldg(reinterpret_cast<const float4*>(sm_row + cbase) + i);
+          t[2 * i] = __ffma2_rn(make_float2(m.x, m.y), make_float2(kLog2e, kLog2e), t[2 * i]);
+          t[2 * i + 1] = __ffma2_rn(make_float2(m.z, m.w), make_float2(kLog2e, kLog2e), t[2 * i + 1]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < kCh / 2; ++i) {
+          const int col = cbase + 2 * i;
+          t[i].x = fmaf(col < Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t[i].x);
+          t[i].y = fmaf(col + 1 < Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t[i].y);
+        }
       }
     }
     // Under the default bias every logit of a chunk is negative: then the sign handling (one
