@@ -10,7 +10,7 @@ import ctypes
 import os
 import threading
 
-from .build import LIB_PATH
+from ._paths import LIB_PATH
 
 SIGATTN_FP16 = 0
 SIGATTN_BF16 = 1

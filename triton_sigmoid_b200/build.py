@@ -13,11 +13,7 @@ import shutil
 import subprocess
 import sys
 
-PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-ROOT = os.path.dirname(PKG_DIR)
-CSRC = os.path.join(PKG_DIR, "csrc")
-LIB_DIR = os.path.join(PKG_DIR, "lib")
-LIB_PATH = os.path.join(LIB_DIR, "libsigattn_b200.so")
+from ._paths import CSRC, LIB_DIR, LIB_PATH, PKG_DIR, ROOT  # noqa: F401
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
