@@ -102,6 +102,20 @@ def test_benchmark_size_against_gpu_fp32_math(causal):
             assert rel_l2(g[b:b + 1], r) <= 1e-2
 
 
+def test_long_sequence_d128_against_gpu_fp32_math():
+    """bf16 causal, N=8192, D=128 (the shape family of the multi-GPU configuration), two heads."""
+    B, T, H, D = 1, 8192, 2, 128
+    q, k, v, do = make_inputs(B, T, T, H, D, torch.bfloat16, std=0.5, seed=3, requires_grad=True)
+    out = m.sigmoid_attention(q, k, v, is_causal=True)
+    out.backward(do)
+    qb, kb, vb = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    ref = m.sigmoid_attention_ref(qb, kb, vb, causal=True, sigmoid_bias=-math.log(T))
+    ref.backward(do.float())
+    assert (out.float() - ref).abs().max().item() <= O_TOL[torch.bfloat16]
+    for g, r in ((q.grad, qb.grad), (k.grad, kb.grad), (v.grad, vb.grad)):
+        assert rel_l2(g, r) <= 1e-2
+
+
 def test_forward_is_deterministic():
     q, k, v, _ = make_inputs(2, 1024, 1024, 4, 64, torch.bfloat16, seed=13)
     assert torch.equal(m.sigmoid_attention(q, k, v, is_causal=True), m.sigmoid_attention(q, k, v, is_causal=True))

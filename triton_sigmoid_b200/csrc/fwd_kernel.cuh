@@ -45,11 +45,15 @@ struct FwdParams {
 #ifndef SIG_FWD_CHUNK
 #define SIG_FWD_CHUNK 32  // score columns per TMEM load of a sigmoid thread (32 measured faster than 16)
 #endif
-constexpr int kFwdSigmoidWarps = 16;
-constexpr int kFwdProducerWarp = 16;
-constexpr int kFwdIssuerWarp = 17;   // S = Q K^T, owns the TMEM allocation
-constexpr int kFwdIssuerWarp2 = 18;  // O += P V
-constexpr int kFwdThreads = 20 * 32;
+#ifndef SIG_FWD_HALVES
+#define SIG_FWD_HALVES 2  // sigmoid warps per (query tile, lane quarter): 2 = each takes 64 of the 128 key columns
+#endif
+constexpr int kFwdHalves = SIG_FWD_HALVES;
+constexpr int kFwdSigmoidWarps = 8 * kFwdHalves;
+constexpr int kFwdProducerWarp = kFwdSigmoidWarps;
+constexpr int kFwdIssuerWarp = kFwdSigmoidWarps + 1;   // S = Q K^T, owns the TMEM allocation
+constexpr int kFwdIssuerWarp2 = kFwdSigmoidWarps + 2;  // O += P V
+constexpr int kFwdThreads = (kFwdSigmoidWarps + 4) * 32;
 constexpr int kFwdBlockM = 256;  // query rows per CTA (two 128-row tiles)
 constexpr int kTileN = 128;      // key rows per step
 
@@ -250,7 +254,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     }
     for (int i = 0; i < kSBufs; ++i) {
       mbar_init(bar(L::kSFull + i), 1);
-      mbar_init(bar(L::kPFull + i), 8);  // one arrival per sigmoid warp of the query tile
+      mbar_init(bar(L::kPFull + i), 4 * kFwdHalves);  // one arrival per sigmoid warp of the query tile
       mbar_init(bar(L::kPvDone + i), 1);
     }
     mbar_init(bar(L::kOFull), 1);
@@ -491,15 +495,17 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     // idle warp
   } else {
     // ============================================================ sigmoid groups + epilogue
-    const int s = warp >> 3;                              // query tile
-    const int g = (warp >> 2) & 1;                        // which half of the key columns
+    const int s = warp / (4 * kFwdHalves);                // query tile
+    const int g = kFwdHalves == 2 ? (warp >> 2) & 1 : 0;  // which half of the key columns (when split)
+    constexpr int kColsMine = 128 / kFwdHalves;           // key columns per thread and job
+    constexpr int kDMine = D / kFwdHalves;                // output columns per thread
     const int lane_row = (warp & 3) * 32 + lane;          // TMEM lane == row within the tile
     const int row = q0 + 128 * s + lane_row;              // query index
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const float c1 = p.scale * kLog2e;
     const float c0 = (p.bias ? p.bias[b] : p.bias_scalar) * kLog2e;
     const float* sm_row = kScoreMod ? (p.score_mod + (int64_t)b * p.Tk) : nullptr;
-    uint8_t* o_row = o_base + 2 * (int64_t)row * p.o_st + g * D;  // this thread's D/2 columns (16-bit)
+    uint8_t* o_row = o_base + 2 * (int64_t)row * p.o_st + g * D;  // this thread's output columns (16-bit)
     const int n_mine = n_kv[s];
     // largest visible key index for this row
     int lim = Lk - 1;
@@ -514,11 +520,12 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       }
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t s_addr = tmem + lane_addr + kColS + 128 * buf + 64 * g;
-      const int col0 = j * kTileN + 64 * g;
-      const bool need_mask = (col0 + 64 > Lk) || (p.causal && col0 + 63 > q0 + 128 * s);
-      // the predicate code exists only in the instantiation used by boundary tiles
-      {
+#pragma unroll
+      for (int hh = 0; hh < kColsMine / 64; ++hh) {
+        const uint32_t s_addr = tmem + lane_addr + kColS + 128 * buf + 64 * (g + hh);
+        const int col0 = j * kTileN + 64 * (g + hh);
+        const bool need_mask = (col0 + 64 > Lk) || (p.causal && col0 + 63 > q0 + 128 * s);
+        // the predicate code exists only in the instantiation used by boundary tiles
         if (need_mask)
           fwd_sigmoid_half_tile<kBF16, kScoreMod, true>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
         else
@@ -536,16 +543,16 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       // this tile is entirely padding (or beyond Tq): zero rows
       if (row < p.Tq) {
 #pragma unroll
-        for (int c = 0; c < D / 16; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < kDMine / 8; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
       }
     } else if (ok) {
       ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kOFull), 0, abort_flag, kSiteBase + 12));
       if (ok) {
         tc_fence_after_sync();
-        const uint32_t o_addr = tmem + lane_addr + kColO + D * s + g * (D / 2);
+        const uint32_t o_addr = tmem + lane_addr + kColO + D * s + g * kDMine;
         const bool live = row < Lq;
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
+        for (int c = 0; c < kDMine / 32; ++c) {
           uint32_t r[32];
           tmem_ld32_sync(o_addr + c * 32, r);
           if (row < p.Tq) {
