@@ -21,10 +21,11 @@
 //                                  red.global.add.f32 per query covers a full 128-byte line;
 //                                D = 64: M = 64 would idle half of the tensor core and half of
 //                                  the lanes, and staging rows in shared memory for bulk
-//                                  the lanes, so each warp regroups its 32 rows x 64 bytes through
-//                                  a private shared-memory patch and adds them with
-//                                  red.global.add.v4.f32, four lanes per 64-byte run (the
-//                                  reduction traffic, not the math, is what bounds this case).
+//                                  the lanes, so each warp takes full 128-byte half rows of every
+//                                  second query row, regrouped through a private shared-memory
+//                                  patch so that eight lanes cover a line, and adds them with
+//                                  red.global.add.v4.f32 (the reduction traffic, not the math,
+//                                  is what bounds this case).
 //
 // Warp roles (20 warps):
 //   warps 0-15  compute: warp w owns TMEM lanes (key rows) 32 (w & 3) .. +31 and the query
@@ -79,11 +80,12 @@ struct BwdSmem {
   static constexpr int kDoOff = kQOff + kStages * kTileBytes;
   static constexpr int kDsOff = kDoOff + kStages * kTileBytes;
   static constexpr int kDsBytes = 128 * 128 * 2;
-  // D = 64 only: a private 32-row x 80-byte patch per compute warp, used to regroup dQ rows so that
-  // four adjacent lanes add 64 consecutive bytes (80 = 64 + 16 keeps the 16-byte accesses off each
-  // other's banks)
+  // D = 64 only: a private patch of 16 rows x 128 bytes per compute warp, used to regroup dQ rows so
+  // that eight adjacent lanes add the 128 bytes of one row (16 bytes of padding per row keep the
+  // 16-byte accesses of different rows off each other's banks)
+  static constexpr int kDqPatchRow = 128 + 16;
   static constexpr int kDqPatchOff = kDsOff + kDsBytes;
-  static constexpr int kDqPatchBytes = (D == 64) ? 32 * 80 : 0;
+  static constexpr int kDqPatchBytes = (D == 64) ? 16 * kDqPatchRow : 0;
   static constexpr int kBarOff = kDqPatchOff + 16 * kDqPatchBytes;
   static constexpr int kKvFull = 0;
   static constexpr int kQFull = 1;                    // [2]
@@ -509,31 +511,35 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
             asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + v * row_stride), "f"(__uint_as_float(r[v])) : "memory");
         }
       } else {
-        uint32_t r[16];
-        tmem_ld16(dq_addr, r);
-        tmem_ld_wait_for(r);
+        // A warp's reduction instructions are served one 128-byte line at a time (~17 clocks each), so
+        // the number of lines a warp touches is what its stall costs.  This warp therefore takes half
+        // of the head dimension (32 columns = one full line per row) of every second row of its lane
+        // quarter: 16 lines per tile, the minimum for 16 warps.  The rows are regrouped through the
+        // warp's shared-memory patch so that eight adjacent lanes cover the 128 bytes of one row.
+        // (Tried and slower: 64-byte runs of all 32 rows; bulk reductions out of shared memory, which
+        // compete with the tile loads for the copy engine; a separate reduction warp, which serialises.)
+        const int col_half = cg & 1, row_par = cg >> 1;
+        uint32_t r[32];
+        tmem_ld32_sync(dq_off - 16 * cg + dq_col(t) + 32 * col_half, r);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(t)));
-        // Lane l holds 64 bytes of row l.  Adding them as they are would make every reduction
-        // instruction touch 32 rows with 16 bytes each, and the L2 handles such half-sector requests
-        // at half its rate.  Through the warp's shared-memory patch the data is regrouped so that lane
-        // l holds bytes 16 (l & 3) .. +15 of rows 8 k + (l >> 2), k = 0..3: four lanes per 64-byte run.
-        // (Bulk reductions out of shared memory, per row or per 256-byte row across warps, measured
-        // slower than this: they compete with the tile loads for the copy engine.)
         uint8_t* patch = smem_gen + L::kDqPatchOff + warp * L::kDqPatchBytes;
-        uint4* mine = reinterpret_cast<uint4*>(patch + lane * 80);
+        if ((lane & 1) == row_par) {
+          uint4* mine = reinterpret_cast<uint4*>(patch + (lane >> 1) * L::kDqPatchRow);
 #pragma unroll
-        for (int m = 0; m < 4; ++m) mine[m] = make_uint4(r[4 * m], r[4 * m + 1], r[4 * m + 2], r[4 * m + 3]);
+          for (int m = 0; m < 8; ++m) mine[m] = make_uint4(r[4 * m], r[4 * m + 1], r[4 * m + 2], r[4 * m + 3]);
+        }
         __syncwarp();
-        const int sub_row = lane >> 2, chunk = lane & 3;
-        float* dst = p.dq_acc + (((int64_t)b * p.Tq + q_tile + quarter * 32 + sub_row) * p.H + h) * D + 16 * cg + 4 * chunk;
-        const int64_t step = (int64_t)8 * p.H * D;  // eight rows further
+        const int slot = lane >> 3, chunk = lane & 7;  // patch row slot (within a group of four) and 16-byte chunk
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint4 w = *reinterpret_cast<const uint4*>(patch + (8 * k + sub_row) * 80 + chunk * 16);
-          if (q_tile + quarter * 32 + 8 * k + sub_row < Lq) {  // queries at or beyond Lq get no gradient
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + k * step), "f"(__uint_as_float(w.x)),
+          const int prow = 4 * k + slot;                                   // patch row = (row within quarter) / 2
+          const int q = q_tile + quarter * 32 + 2 * prow + row_par;
+          const uint4 w = *reinterpret_cast<const uint4*>(patch + prow * L::kDqPatchRow + chunk * 16);
+          if (q < Lq) {  // queries at or beyond Lq get no gradient
+            float* dst = p.dq_acc + (((int64_t)b * p.Tq + q) * p.H + h) * D + 32 * col_half + 4 * chunk;
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(w.x)),
                          "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
                          : "memory");
           }
