@@ -1,5 +1,7 @@
-// Forward kernel: O = sigmoid(scale * Q K^T + bias) V for one (batch, head, 256-query block)
-// per CTA.
+// Forward kernel: O = sigmoid(scale * Q K^T + bias) V.  A work item is one (batch, head,
+// 256-query block); the kernel is persistent: one CTA per SM takes items from a ticket counter
+// until none are left, so that loads and scores of the next item overlap the epilogue of the
+// current one and uneven items (causal, ragged lengths) balance themselves.
 //
 // Takes over the work of the reference's _fwd_dense_kernel
 // (src/triton_sigmoid/sigmoid_triton_dense.py:23-154) and _fwd_padded_kernel
@@ -9,12 +11,11 @@
 //   warps 0-7    sigmoid groups of query tile 0 (rows [q0, q0+128)): warps 0-3 take key columns
 //                [0,64) of every score tile, warps 4-7 columns [64,128); one thread per row
 //   warps 8-15   the same for query tile 1 (rows [q0+128, q0+256))
-//   warp  16     TMA producer: Q tiles once, then K_j / V_j through a ring of smem stages
+//   warp  16     item scheduler + TMA producer: Q tiles per item, K_j / V_j through a ring of smem stages
 //   warp  17     tcgen05 issuer 1: S = Q_s K_j^T (smem x smem -> TMEM fp32); owns the TMEM allocation
 //   warp  18     tcgen05 issuer 2: O_s += P V_j (TMEM x smem -> TMEM fp32)
-//   warp  19     idle
 // There is no row normaliser in sigmoid attention, so O simply accumulates in TMEM over the
-// whole key loop.  The (query tile, key tile) jobs are processed in a fixed order through a
+// whole key loop of an item.  The (query tile, key tile) jobs are processed in a fixed order through a
 // small ring of S buffers in TMEM (3 when D = 64, 2 when D = 128): the issuer computes the
 // scores of a later job while the sigmoid groups turn earlier ones into 16-bit P in place
 // (each group writes P over the start of the columns it has just read) and signal the issuer.
@@ -39,7 +40,11 @@ struct FwdParams {
   float bias_scalar;
   int B, H, Tq, Tk;
   int causal;
-  int n_qblk;  // ceil(Tq / 256)
+  int n_qblk;   // ceil(Tq / 256)
+  int n_items;  // B * H * n_qblk
+  // two counters, zero between launches: [0] items handed out beyond the first per CTA,
+  // [1] CTAs that have finished (the last one clears both)
+  unsigned int* ticket;
 };
 
 #ifndef SIG_FWD_CHUNK
@@ -53,7 +58,16 @@ constexpr int kFwdSigmoidWarps = 8 * kFwdHalves;
 constexpr int kFwdProducerWarp = kFwdSigmoidWarps;
 constexpr int kFwdIssuerWarp = kFwdSigmoidWarps + 1;   // S = Q K^T, owns the TMEM allocation
 constexpr int kFwdIssuerWarp2 = kFwdSigmoidWarps + 2;  // O += P V
-constexpr int kFwdThreads = (kFwdSigmoidWarps + 4) * 32;
+constexpr int kFwdThreads = (kFwdSigmoidWarps + 4) * 32;  // the role warps form a register-allocation group of four
+constexpr int kFwdLaunchRegs = 96;  // what 640 threads per CTA get each: 65536 / 640, rounded down to a multiple of 8
+// Registers per thread after the re-allocation: the role warps (a group of four) and the sigmoid warps.
+// D = 64: the role warps fit in 32; D = 128: the single issuing warp carries two job cursors.
+template <int D> struct FwdRegs {
+  static constexpr int kRole = (D == 64) ? 32 : 64;
+  static constexpr int kSigmoid = (D == 64) ? 112 : 104;
+  static_assert(kFwdSigmoidWarps * 32 * kSigmoid + 128 * kRole <= kFwdThreads * kFwdLaunchRegs,
+                "the re-allocation may not ask for more registers than the CTA holds");
+};
 constexpr int kFwdBlockM = 256;  // query rows per CTA (two 128-row tiles)
 constexpr int kTileN = 128;      // key rows per step
 
@@ -75,10 +89,14 @@ struct FwdSmem {
   static constexpr int kSFull = kVEmpty + kStages;    // [kSBufs]
   static constexpr int kPFull = kSFull + kSBufs;      // [kSBufs]
   static constexpr int kOFull = kPFull + kSBufs;      // [1]
-  static constexpr int kVFix = kOFull + 1;            // [1] padded rows of the last V tile zeroed
-  static constexpr int kPvDone = kVFix + 1;           // [kSBufs] P V product of the buffer's job complete
-  static constexpr int kNumBars = kPvDone + kSBufs;
-  static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int)
+  static constexpr int kVFix = kOFull + 1;            // [kStages] padded rows of the stage's V tile zeroed
+  static constexpr int kPvDone = kVFix + kStages;     // [kSBufs] P V product of the buffer's job complete
+  static constexpr int kQEmpty = kPvDone + kSBufs;    // [1] all score products of the item issued and complete
+  static constexpr int kOEmpty = kQEmpty + 1;         // [1] O of the item read out of TMEM
+  static constexpr int kItemFull = kOEmpty + 1;       // [2] item index published
+  static constexpr int kItemEmpty = kItemFull + 2;    // [2] item index read by every consumer warp
+  static constexpr int kNumBars = kItemEmpty + 2;
+  static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int), item ring (2 int)
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynBytes = kTotal + 1024;  // slack to align the base to 1024 bytes
 };
@@ -92,6 +110,12 @@ struct FwdCursor {
   int buf;      // S buffer of the job
   uint32_t bph; // parity of that buffer's barriers
   bool fresh;   // first job that touches key tile j
+  // start of a new item: stage and buffer positions carry over from the previous item
+  __device__ __forceinline__ void begin_item(int n0) {
+    s = (n0 > 0) ? 0 : 1;
+    j = 0;
+    fresh = true;
+  }
   __device__ __forceinline__ void advance(int n0, int n1, int n_stages, int n_bufs) {
     if (s == 0 && j < n1) {
       s = 1;
@@ -172,6 +196,38 @@ __device__ __forceinline__ void fwd_sigmoid_half_tile(uint32_t s_addr, float c1,
   }
 }
 
+// One work item, decoded the same way by every warp role.
+struct FwdItem {
+  int b, h, q0;
+  int Lq, Lk;
+  int n0, n1, n_max;  // key tiles of query tile 0 / 1, and the larger of the two
+};
+__device__ __forceinline__ FwdItem fwd_decode_item(const FwdParams& p, int item) {
+  FwdItem it;
+  const int bh = item / p.n_qblk;
+  const int qi = item - bh * p.n_qblk;
+  it.b = bh / p.H;
+  it.h = bh - it.b * p.H;
+  const int qblk = p.causal ? (p.n_qblk - 1 - qi) : qi;  // heavy blocks of a head first
+  it.q0 = qblk * kFwdBlockM;
+  it.Lq = p.Tq;
+  it.Lk = p.Tk;
+  if (p.lens_q) it.Lq = min(max(p.lens_q[it.b], 0), p.Tq);
+  if (p.lens_k) it.Lk = min(max(p.lens_k[it.b], 0), p.Tk);
+  int n_kv[2];
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    const int r0 = it.q0 + 128 * s;
+    int kv_end = it.Lk;
+    if (p.causal) kv_end = min(kv_end, r0 + 128);
+    n_kv[s] = (r0 < it.Lq) ? (kv_end + kTileN - 1) / kTileN : 0;
+  }
+  it.n0 = n_kv[0];
+  it.n1 = n_kv[1];
+  it.n_max = max(it.n0, it.n1);
+  return it;
+}
+
 template <int D, bool kBF16, bool kScoreMod>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
@@ -187,6 +243,8 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   // D = 64: scores and P V are issued by two warps (the issue stream bounds the kernel); D = 128:
   // one warp issues both, in order - with only two S buffers the extra barrier hop costs more
   constexpr bool kSplitIssue = (D == 64);
+  // warps that read the published item index: the sigmoid warps and the issuing warp(s)
+  constexpr int kItemReaders = kFwdSigmoidWarps + (kSplitIssue ? 2 : 1);
   static_assert(kColO + 2 * D <= kTmemCols, "TMEM budget");
 
   extern __shared__ uint8_t smem_dyn[];
@@ -196,47 +254,10 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   auto bar = [&](int slot) -> uint32_t { return bars + 8u * slot; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
+  volatile int* item_ring = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 8);  // [2]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-
-  // ---------------------------------------------------------------- work item
-  const int qblk = p.causal ? (p.n_qblk - 1 - (int)blockIdx.x) : (int)blockIdx.x;  // heavy blocks first
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
-  const int q0 = qblk * kFwdBlockM;
-  int Lq = p.Tq, Lk = p.Tk;
-  if (p.lens_q) Lq = min(max(p.lens_q[b], 0), p.Tq);
-  if (p.lens_k) Lk = min(max(p.lens_k[b], 0), p.Tk);
-
-  // key-tile counts per query tile
-  int n_kv[2];
-#pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    const int r0 = q0 + 128 * s;
-    int kv_end = Lk;
-    if (p.causal) kv_end = min(kv_end, r0 + 128);
-    n_kv[s] = (r0 < Lq) ? (kv_end + kTileN - 1) / kTileN : 0;
-  }
-  const int n0 = n_kv[0], n1 = n_kv[1];
-  const int n_max = max(n0, n1);
-  // Jobs are ordered by key tile, query tile 0 before 1: (0,0) (1,0) (0,1) (1,1) ...
-  // Index of job (s, j) in that order (only meaningful when j < n_kv[s]).
-  auto job_index = [&](int s, int j) { return s == 0 ? j + min(j, n1) : j + min(j + 1, n0); };
-
-  uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) + 2 * ((int64_t)b * p.o_sb + (int64_t)h * p.o_sh);
-
-  if (n_max == 0) {
-    // nothing visible to this block: the reference stores zeros for such rows
-    constexpr int kChunksPerRow = D * 2 / 16;
-    for (int i = threadIdx.x; i < kFwdBlockM * kChunksPerRow; i += kFwdThreads) {
-      const int row = q0 + i / kChunksPerRow;
-      if (row < p.Tq)
-        *reinterpret_cast<uint4*>(o_base + 2 * (int64_t)row * p.o_st + 16 * (i % kChunksPerRow)) =
-            make_uint4(0, 0, 0, 0);
-    }
-    return;
-  }
 
   // a kernel of this library already gave up on a wait: do not pile more work on a sick device
   if (*reinterpret_cast<volatile int*>(&g_status_word) != 0) return;
@@ -258,7 +279,13 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       mbar_init(bar(L::kPvDone + i), 1);
     }
     mbar_init(bar(L::kOFull), 1);
-    mbar_init(bar(L::kVFix), 1);
+    for (int i = 0; i < kStages; ++i) mbar_init(bar(L::kVFix + i), 1);
+    mbar_init(bar(L::kQEmpty), 1);
+    mbar_init(bar(L::kOEmpty), kFwdSigmoidWarps);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(L::kItemFull + i), 1);
+      mbar_init(bar(L::kItemEmpty + i), kItemReaders);
+    }
     fence_mbar_init();
   }
   if (warp == kFwdProducerWarp && lane == 0) {
@@ -275,111 +302,172 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
+  // The sigmoid warps hold 64 scores each in flight and want more registers than an even split
+  // gives; the four role warps need few.  Registers only move within what the CTA was given at
+  // launch, so the two counts must add up to no more than that (else the increase never returns).
+
+  // Consumer side of the item ring: returns the k-th item of this CTA, or -1 when there is none
+  // (also on a failed wait).  Called by all 32 lanes of a reader warp.
+  auto read_item = [&](int k) -> int {
+    const int slot = k & 1;
+    if (!mbar_wait_warp(bar(L::kItemFull + slot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30)) return -1;
+    const int item = item_ring[slot];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(L::kItemEmpty + slot));
+    return item;
+  };
+
+  if (warp >= kFwdSigmoidWarps) {
+  // All four role warps (the idle one included) execute this one instruction: the release is an
+  // operation of the whole group of four.
+  setmaxnreg_dec<FwdRegs<D>::kRole>();
   if (warp == kFwdProducerWarp) {
-    // ============================================================ TMA producer
-    if (lane == 0) {
+    // ============================================================ item scheduler + TMA producer
+    int tile = 0;        // key tiles loaded so far (all items): position in the stage ring
+    int act = 0;         // items with work so far
+    bool ok = true;
+    for (int k = 0; ok; ++k) {
+      const int slot = k & 1;
+      ok = mbar_wait_warp(bar(L::kItemEmpty + slot), ((uint32_t)(k >> 1) & 1u) ^ 1u, abort_flag, kSiteBase + 31);
+      if (!ok) break;
+      int item = blockIdx.x;  // the first item needs no ticket
+      if (lane == 0) {
+        if (k > 0) {
+          const unsigned int t = atomicAdd(p.ticket, 1u) + gridDim.x;
+          item = t < (unsigned int)p.n_items ? (int)t : -1;
+        }
+        item_ring[slot] = item;
+        mbar_arrive(bar(L::kItemFull + slot));
+      }
+      item = __shfl_sync(0xffffffffu, item, 0);
+      if (item < 0) break;
+      const FwdItem it = fwd_decode_item(p, item);
+      if (it.n_max == 0) continue;
+
+      // Q tiles of this item: the previous item's score products must have read theirs
+      if (act > 0) ok = mbar_wait_warp(bar(L::kQEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 32);
+      if (!ok) break;
+      if (lane == 0) {
 #pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        if (n_kv[s] > 0) {
-          mbar_expect_tx(bar(L::kQFull + s), kTileBytes);
+        for (int s = 0; s < 2; ++s) {
+          if ((s == 0 ? it.n0 : it.n1) > 0) {
+            mbar_expect_tx(bar(L::kQFull + s), kTileBytes);
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(smem_base + L::kQOff + s * kTileBytes + c * 16384, &q_map, bar(L::kQFull + s), c * 64, it.h,
+                          it.q0 + 128 * s, it.b);
+          }
+        }
+      }
+      int st = tile % kStages;
+      uint32_t ph = (uint32_t)(tile / kStages) & 1u;
+      for (int j = 0; j < it.n_max && ok; ++j) {
+        ok = mbar_wait_warp(bar(L::kKEmpty + st), ph ^ 1u, abort_flag, kSiteBase + 1);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(bar(L::kKFull + st), kTileBytes);
 #pragma unroll
           for (int c = 0; c < D / 64; ++c)
-            tma_load_4d(smem_base + L::kQOff + s * kTileBytes + c * 16384, &q_map, bar(L::kQFull + s), c * 64, h,
-                        q0 + 128 * s, b);
+            tma_load_4d(smem_base + L::kKOff + st * kTileBytes + c * 16384, &k_map, bar(L::kKFull + st), c * 64, it.h,
+                        j * kTileN, it.b);
         }
-      }
-    }
-    bool ok = true;
-    for (int j = 0; j < n_max && ok; ++j) {
-      const int st = j % kStages;
-      const uint32_t ph = (j / kStages) & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kKEmpty + st), ph ^ 1, abort_flag, kSiteBase + 1));
-      if (!ok) break;
-      if (lane == 0) {
-        mbar_expect_tx(bar(L::kKFull + st), kTileBytes);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem_base + L::kKOff + st * kTileBytes + c * 16384, &k_map, bar(L::kKFull + st), c * 64, h,
-                      j * kTileN, b);
-      }
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kVEmpty + st), ph ^ 1, abort_flag, kSiteBase + 2));
-      if (!ok) break;
-      if (lane == 0) {
-        mbar_expect_tx(bar(L::kVFull + st), kTileBytes);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem_base + L::kVOff + st * kTileBytes + c * 16384, &v_map, bar(L::kVFull + st), c * 64, h,
-                      j * kTileN, b);
-      }
-      if (j * kTileN + kTileN > Lk) {
-        // The tile straddles the valid key length.  P is zero for the padded keys, but 0 * NaN
-        // is NaN inside the MMA, so whatever sits in the padded V rows must be cleared first.
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kVFull + st), ph, abort_flag, kSiteBase + 13));
+        ok = mbar_wait_warp(bar(L::kVEmpty + st), ph ^ 1u, abort_flag, kSiteBase + 2);
         if (!ok) break;
-        const int first_bad = Lk - j * kTileN;  // in [1, 127]
-        uint8_t* vt = smem_gen + L::kVOff + st * kTileBytes;
-        // each row is one 128-byte line per 64-column block; the swizzle only permutes within a line
-        for (int i = lane; i < (kTileN - first_bad) * 8 * (D / 64); i += 32) {
-          const int c = i / ((kTileN - first_bad) * 8);
-          const int rem = i % ((kTileN - first_bad) * 8);
-          const int r = first_bad + rem / 8;
-          *reinterpret_cast<uint4*>(vt + c * 16384 + r * 128 + (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
+        if (lane == 0) {
+          mbar_expect_tx(bar(L::kVFull + st), kTileBytes);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(smem_base + L::kVOff + st * kTileBytes + c * 16384, &v_map, bar(L::kVFull + st), c * 64, it.h,
+                        j * kTileN, it.b);
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kVFix));
+        if (j * kTileN + kTileN > it.Lk) {
+          // The tile straddles the valid key length.  P is zero for the padded keys, but 0 * NaN
+          // is NaN inside the MMA, so whatever sits in the padded V rows must be cleared first.
+          ok = mbar_wait_warp(bar(L::kVFull + st), ph, abort_flag, kSiteBase + 13);
+          if (!ok) break;
+          const int first_bad = it.Lk - j * kTileN;  // in [1, 127]
+          uint8_t* vt = smem_gen + L::kVOff + st * kTileBytes;
+          // each row is one 128-byte line per 64-column block; the swizzle only permutes within a line
+          for (int i = lane; i < (kTileN - first_bad) * 8 * (D / 64); i += 32) {
+            const int c = i / ((kTileN - first_bad) * 8);
+            const int rem = i % ((kTileN - first_bad) * 8);
+            const int r = first_bad + rem / 8;
+            *reinterpret_cast<uint4*>(vt + c * 16384 + r * 128 + (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(L::kVFix + st));
+        }
+        if (++st == kStages) { st = 0; ph ^= 1u; }
       }
+      tile += it.n_max;
+      ++act;
     }
-  } else if (warp == kFwdIssuerWarp) {
+  }
+  else if (warp == kFwdIssuerWarp) {
     if constexpr (kSplitIssue) {
     // ============================================================ tcgen05 issuer 1: S = Q K^T
     // Two issuing warps (this one for the scores, the next for P V): an issuing warp's
     // instruction stream is one long dependent chain (waits, MMAs, commits), and a single warp
     // doing both products was what bounded the kernel.  All ring positions, stage numbers and
-    // barrier parities are carried incrementally (no division, no modulo), and descriptors are a
-    // precomputed base plus a constant in the start-address field.
+    // barrier parities are carried incrementally (no division, no modulo) and run on across
+    // items; descriptors are a precomputed base plus a constant in the start-address field.
     const bool leader = elect_one();
     constexpr uint32_t idesc_qk = make_idesc(128, 128, kBF16, false, false);
     constexpr uint32_t kStageStep = kTileBytes >> 4;  // one smem stage, in descriptor address units
-    const int n_jobs = n0 + n1;
     // Q tile 0 and K stage 0: rows = M/N, the 64 contiguous elements = contraction
     const uint64_t q_desc0 = smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
     const uint64_t k_desc0 = smem_desc_sw128(smem_base + L::kKOff, 16, 1024);
     const uint32_t q_lo = (uint32_t)q_desc0, k_lo = (uint32_t)k_desc0, hi = (uint32_t)(q_desc0 >> 32);
-    FwdCursor c{(n0 > 0) ? 0 : 1, 0, 0, 0u, 0, 0u, true};
+    FwdCursor c{0, 0, 0, 0u, 0, 0u, true};
+    uint32_t q_par0 = 0u, q_par1 = 0u;  // parity of each Q tile's "full" barrier
+    int total = 0;                 // jobs issued so far, saturating at kSBufs
     bool ok = true;
-    for (int n = 0; n < n_jobs && ok; ++n) {
-      if (c.j == 0) ok = mbar_wait_warp(bar(L::kQFull + c.s), 0, abort_flag, kSiteBase + 3);
-      if (c.fresh) ok = ok && mbar_wait_warp(bar(L::kKFull + c.st), c.ph, abort_flag, kSiteBase + 5);
-      // the buffer still holds the probabilities of job n - kSBufs until their P V product is complete
-      if (n >= kSBufs) ok = ok && mbar_wait_warp(bar(L::kPvDone + c.buf), c.bph ^ 1u, abort_flag, kSiteBase + 4);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t qa = q_lo + (uint32_t)c.s * kStageStep;
-      const uint32_t ka = k_lo + (uint32_t)c.st * kStageStep;
-      const uint32_t dst = tmem + kColS + 128u * (uint32_t)c.buf;
+    for (int k = 0; ok; ++k) {
+      const int item = read_item(k);
+      if (item < 0) break;
+      const FwdItem it = fwd_decode_item(p, item);
+      if (it.n_max == 0) continue;
+      const int n0 = it.n0, n1 = it.n1;
+      const int n_jobs = n0 + n1;
+      c.begin_item(n0);
+      for (int n = 0; n < n_jobs && ok; ++n) {
+        if (c.j == 0) ok = mbar_wait_warp(bar(L::kQFull + c.s), (c.s ? q_par1 : q_par0), abort_flag, kSiteBase + 3);
+        if (c.fresh) ok = ok && mbar_wait_warp(bar(L::kKFull + c.st), c.ph, abort_flag, kSiteBase + 5);
+        // the buffer still holds the probabilities of the job kSBufs earlier until their P V product is complete
+        if (total >= kSBufs) ok = ok && mbar_wait_warp(bar(L::kPvDone + c.buf), c.bph ^ 1u, abort_flag, kSiteBase + 4);
+        else ++total;
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t qa = q_lo + (uint32_t)c.s * kStageStep;
+        const uint32_t ka = k_lo + (uint32_t)c.st * kStageStep;
+        const uint32_t dst = tmem + kColS + 128u * (uint32_t)c.buf;
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t off = (uint32_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
-        mma_ss(leader, dst, make_desc(qa + off, hi), make_desc(ka + off, hi), idesc_qk, kk > 0);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (uint32_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          mma_ss(leader, dst, make_desc(qa + off, hi), make_desc(ka + off, hi), idesc_qk, kk > 0);
+        }
+        mma_commit(leader, bar(L::kSFull + c.buf));
+        // last job that reads K_j: hand the stage back to the producer
+        if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kKEmpty + c.st));
+        c.advance(n0, n1, kStages, kSBufs);
       }
-      mma_commit(leader, bar(L::kSFull + c.buf));
-      // last job that reads K_j: hand the stage back to the producer
-      if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kKEmpty + c.st));
-      c.advance(n0, n1, kStages, kSBufs);
+      if (!ok) break;
+      mma_commit(leader, bar(L::kQEmpty));  // the Q tiles may be overwritten once these products are complete
+      if (n0 > 0) q_par0 ^= 1u;
+      if (n1 > 0) q_par1 ^= 1u;
     }
     } else {
     // ============================================================ single tcgen05 issuer (D = 128)
     // This warp's instruction stream is one long dependent chain, so its length per job decides
     // how quickly finished probabilities turn into new scores: all ring positions, stage numbers
-    // and barrier parities are carried incrementally (no division, no modulo), and descriptors
-    // are a precomputed base plus a constant in the start-address field.
+    // and barrier parities are carried incrementally (no division, no modulo) and run on across
+    // items; descriptors are a precomputed base plus a constant in the start-address field.
     {
       const bool leader = elect_one();
       constexpr uint32_t idesc_qk = make_idesc(128, 128, kBF16, false, false);
       constexpr uint32_t idesc_pv = make_idesc(128, D, kBF16, false, true);
       constexpr uint32_t kStageStep = kTileBytes >> 4;  // one smem stage, in descriptor address units
-      const int n_jobs = n0 + n1;
       bool ok = true;
       // Q tile 0, K stage 0 (rows = M/N, the 64 contiguous elements = K) and V stage 0 (rows = K,
       // the 64 contiguous elements = N, next 64-column block 16 KB further)
@@ -390,15 +478,17 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const uint32_t k_lo = (uint32_t)k_desc0, k_hi = (uint32_t)(k_desc0 >> 32);
       const uint32_t v_lo = (uint32_t)v_desc0, v_hi = (uint32_t)(v_desc0 >> 32);
 
-      FwdCursor cs{(n0 > 0) ? 0 : 1, 0, 0, 0u, 0, 0u, true};  // next scores to issue
-      FwdCursor cp = cs;                                      // next P V product to issue
+      FwdCursor cs{0, 0, 0, 0u, 0, 0u, true};  // next scores to issue
+      FwdCursor cp = cs;                       // next P V product to issue
+      uint32_t q_par0 = 0u, q_par1 = 0u;       // parity of each Q tile's "full" barrier
+      uint32_t fix_par = 0u;                   // bit st: parity of stage st's "padded V rows cleared" barrier
+      int act = 0;                             // items with work so far
+      int n0 = 0, n1 = 0, Lk = 0;
 
       // S[buf] = Q_s K_j^T
       auto issue_s = [&](const FwdCursor& c) {
-        {
-          if (c.j == 0) ok = ok && mbar_wait_warp(bar(L::kQFull + c.s), 0, abort_flag, kSiteBase + 3);
-          if (c.fresh) ok = ok && mbar_wait_warp(bar(L::kKFull + c.st), c.ph, abort_flag, kSiteBase + 5);
-        }
+        if (c.j == 0) ok = ok && mbar_wait_warp(bar(L::kQFull + c.s), (c.s ? q_par1 : q_par0), abort_flag, kSiteBase + 3);
+        if (c.fresh) ok = ok && mbar_wait_warp(bar(L::kKFull + c.st), c.ph, abort_flag, kSiteBase + 5);
         if (!ok) return;
         const uint32_t qa = q_lo + (uint32_t)c.s * kStageStep;
         const uint32_t ka = k_lo + (uint32_t)c.st * kStageStep;
@@ -414,14 +504,14 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       };
       // O_s += P[buf] V_j
       auto issue_pv = [&](const FwdCursor& c) {
-        {
-          if (c.fresh) {
-            ok = ok && mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
-            if (c.j * kTileN + kTileN > Lk)  // padded V rows are being cleared by the producer warp
-              ok = ok && mbar_wait_warp(bar(L::kVFix), 0, abort_flag, kSiteBase + 14);
+        if (c.fresh) {
+          ok = ok && mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
+          if (c.j * kTileN + kTileN > Lk) {  // padded V rows are being cleared by the producer warp
+            ok = ok && mbar_wait_warp(bar(L::kVFix + c.st), (fix_par >> c.st) & 1u, abort_flag, kSiteBase + 14);
+            fix_par ^= 1u << c.st;
           }
-          ok = ok && mbar_wait_warp(bar(L::kPFull + c.buf), c.bph, abort_flag, kSiteBase + 7);
         }
+        ok = ok && mbar_wait_warp(bar(L::kPFull + c.buf), c.bph, abort_flag, kSiteBase + 7);
         if (!ok) return;
         tc_fence_after_sync();
         const uint32_t va = v_lo + (uint32_t)c.st * kStageStep;
@@ -437,21 +527,39 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
       };
 
-      int n_s = 0;
-      for (; n_s < kSBufs && n_s < n_jobs && ok; ++n_s) {
-        issue_s(cs);
-        cs.advance(n0, n1, kStages, kSBufs);
-      }
-      for (int n = 0; n < n_jobs && ok; ++n) {
-        issue_pv(cp);
-        cp.advance(n0, n1, kStages, kSBufs);
-        if (n_s < n_jobs && ok) {
-          issue_s(cs);  // reuses the buffer the product above has just consumed
+      for (int k = 0; ok; ++k) {
+        const int item = read_item(k);
+        if (item < 0) break;
+        const FwdItem it = fwd_decode_item(p, item);
+        if (it.n_max == 0) continue;
+        n0 = it.n0;
+        n1 = it.n1;
+        Lk = it.Lk;
+        const int n_jobs = n0 + n1;
+        cs.begin_item(n0);
+        cp.begin_item(n0);
+        int n_s = 0;
+        // scores of the next job; after the item's last ones the Q tiles may be overwritten, which
+        // lets the producer fetch the next item's while the remaining products run
+        auto next_s = [&]() {
+          issue_s(cs);
           cs.advance(n0, n1, kStages, kSBufs);
-          ++n_s;
+          if (++n_s == n_jobs && ok) mma_commit(leader, bar(L::kQEmpty));
+        };
+        while (n_s < kSBufs && n_s < n_jobs && ok) next_s();
+        // the accumulators still hold the previous item's O until the sigmoid warps have read it
+        if (act > 0) ok = ok && mbar_wait_warp(bar(L::kOEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 33);
+        for (int n = 0; n < n_jobs && ok; ++n) {
+          issue_pv(cp);
+          cp.advance(n0, n1, kStages, kSBufs);
+          if (n_s < n_jobs && ok) next_s();  // reuses the buffer the product above has just consumed
         }
+        if (!ok) break;
+        mma_commit(leader, bar(L::kOFull));
+        if (n0 > 0) q_par0 ^= 1u;
+        if (n1 > 0) q_par1 ^= 1u;
+        ++act;
       }
-      if (ok) mma_commit(leader, bar(L::kOFull));
     }
     }
   } else if (warp == kFwdIssuerWarp2) {
@@ -460,115 +568,174 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     const bool leader = elect_one();
     constexpr uint32_t idesc_pv = make_idesc(128, D, kBF16, false, true);
     constexpr uint32_t kStageStep = kTileBytes >> 4;
-    const int n_jobs = n0 + n1;
     // V stage 0: rows = contraction, the 64 contiguous elements = N, next 64-column block 16 KB further
     const uint64_t v_desc0 = smem_desc_sw128(smem_base + L::kVOff, 16384, 1024);
     const uint32_t v_lo = (uint32_t)v_desc0, hi = (uint32_t)(v_desc0 >> 32);
-    FwdCursor c{(n0 > 0) ? 0 : 1, 0, 0, 0u, 0, 0u, true};
+    FwdCursor c{0, 0, 0, 0u, 0, 0u, true};
+    uint32_t fix_par = 0u;  // bit st: parity of stage st's "padded V rows cleared" barrier
+    int act = 0;            // items with work so far
     bool ok = true;
-    for (int n = 0; n < n_jobs && ok; ++n) {
-      if (c.fresh) {
-        ok = mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
-        if (c.j * kTileN + kTileN > Lk)  // padded V rows are being cleared by the producer warp
-          ok = ok && mbar_wait_warp(bar(L::kVFix), 0, abort_flag, kSiteBase + 14);
-      }
-      ok = ok && mbar_wait_warp(bar(L::kPFull + c.buf), c.bph, abort_flag, kSiteBase + 7);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t va = v_lo + (uint32_t)c.st * kStageStep;
-      const uint32_t pa = tmem + kColS + 128u * (uint32_t)c.buf;
-      const uint32_t dst = tmem + kColO + (uint32_t)(D * c.s);
-      const uint32_t acc0 = c.j > 0 ? 1u : 0u;
+    for (int k = 0; ok; ++k) {
+      const int item = read_item(k);
+      if (item < 0) break;
+      const FwdItem it = fwd_decode_item(p, item);
+      if (it.n_max == 0) continue;
+      const int n0 = it.n0, n1 = it.n1;
+      const int n_jobs = n0 + n1;
+      c.begin_item(n0);
+      // the accumulators still hold the previous item's O until the sigmoid warps have read it
+      if (act > 0) ok = mbar_wait_warp(bar(L::kOEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 33);
+      for (int n = 0; n < n_jobs && ok; ++n) {
+        if (c.fresh) {
+          ok = mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
+          if (c.j * kTileN + kTileN > it.Lk) {  // padded V rows are being cleared by the producer warp
+            ok = ok && mbar_wait_warp(bar(L::kVFix + c.st), (fix_par >> c.st) & 1u, abort_flag, kSiteBase + 14);
+            fix_par ^= 1u << c.st;
+          }
+        }
+        ok = ok && mbar_wait_warp(bar(L::kPFull + c.buf), c.bph, abort_flag, kSiteBase + 7);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t va = v_lo + (uint32_t)c.st * kStageStep;
+        const uint32_t pa = tmem + kColS + 128u * (uint32_t)c.buf;
+        const uint32_t dst = tmem + kColO + (uint32_t)(D * c.s);
+        const uint32_t acc0 = c.j > 0 ? 1u : 0u;
 #pragma unroll
-      for (int kk = 0; kk < kTileN / 16; ++kk) {
-        // P of key columns [64g, 64g+64) sits, 16-bit packed, in buffer columns 64g + [0,32)
-        mma_ts(leader, dst, pa + 64 * (kk >> 2) + 8 * (kk & 3), make_desc(va + kk * (2048 >> 4), hi), idesc_pv,
-               kk > 0 ? 1u : acc0);
+        for (int kk = 0; kk < kTileN / 16; ++kk) {
+          // P of key columns [64g, 64g+64) sits, 16-bit packed, in buffer columns 64g + [0,32)
+          mma_ts(leader, dst, pa + 64 * (kk >> 2) + 8 * (kk & 3), make_desc(va + kk * (2048 >> 4), hi), idesc_pv,
+                 kk > 0 ? 1u : acc0);
+        }
+        mma_commit(leader, bar(L::kPvDone + c.buf));
+        if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
+        c.advance(n0, n1, kStages, kSBufs);
       }
-      mma_commit(leader, bar(L::kPvDone + c.buf));
-      if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
-      c.advance(n0, n1, kStages, kSBufs);
+      if (!ok) break;
+      mma_commit(leader, bar(L::kOFull));
+      ++act;
     }
-    if (ok) mma_commit(leader, bar(L::kOFull));
     }
-  } else if (warp >= kFwdSigmoidWarps) {
-    // idle warp
-  } else {
+  }
+  }  // role warps
+  else {
     // ============================================================ sigmoid groups + epilogue
+    setmaxnreg_inc<FwdRegs<D>::kSigmoid>();
     const int s = warp / (4 * kFwdHalves);                // query tile
     const int g = kFwdHalves == 2 ? (warp >> 2) & 1 : 0;  // which half of the key columns (when split)
     constexpr int kColsMine = 128 / kFwdHalves;           // key columns per thread and job
     constexpr int kDMine = D / kFwdHalves;                // output columns per thread
     const int lane_row = (warp & 3) * 32 + lane;          // TMEM lane == row within the tile
-    const int row = q0 + 128 * s + lane_row;              // query index
-    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c1 = p.scale * kLog2e;
-    const float c0 = (p.bias ? p.bias[b] : p.bias_scalar) * kLog2e;
-    const float* sm_row = kScoreMod ? (p.score_mod + (int64_t)b * p.Tk) : nullptr;
-    uint8_t* o_row = o_base + 2 * (int64_t)row * p.o_st + g * D;  // this thread's output columns (16-bit)
-    const int n_mine = n_kv[s];
-    // largest visible key index for this row
-    int lim = Lk - 1;
-    if (p.causal) lim = min(lim, row);
+    int jobs_base = 0;  // jobs of all earlier items: position of this item's first job in the S ring
+    int act = 0;        // items with work so far
     bool ok = true;
 
-    for (int j = 0; j < n_mine; ++j) {
-      const int n = job_index(s, j);
-      const int buf = n % kSBufs;
-      {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kSFull + buf), (n / kSBufs) & 1, abort_flag, kSiteBase + 10 + s));
-      }
+    for (int k = 0; ok; ++k) {
+      // The ring slot keeps the item until this warp releases it at the end of the item, so what
+      // only the epilogue needs is decoded again there instead of being held in registers.
+      const int slot = k & 1;
+      ok = mbar_wait_warp(bar(L::kItemFull + slot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30);
       if (!ok) break;
-      tc_fence_after_sync();
-#pragma unroll
-      for (int hh = 0; hh < kColsMine / 64; ++hh) {
-        const uint32_t s_addr = tmem + lane_addr + kColS + 128 * buf + 64 * (g + hh);
-        const int col0 = j * kTileN + 64 * (g + hh);
-        const bool need_mask = (col0 + 64 > Lk) || (p.causal && col0 + 63 > q0 + 128 * s);
-        // the predicate code exists only in the instantiation used by boundary tiles
-        if (need_mask)
-          fwd_sigmoid_half_tile<kBF16, kScoreMod, true>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
-        else
-          fwd_sigmoid_half_tile<kBF16, kScoreMod, false>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
-      }
+      const int item = item_ring[slot];
+      if (item < 0) break;
+      int n0, n1, n_mine, lim, mask_from;
+      float c0;
+      const float* sm_row = nullptr;
       {
+        const FwdItem it = fwd_decode_item(p, item);
+        n0 = it.n0;
+        n1 = it.n1;
+        n_mine = s == 0 ? n0 : n1;
+        const int row = it.q0 + 128 * s + lane_row;  // query index
+        // largest visible key index for this row
+        lim = it.Lk - 1;
+        if (p.causal) lim = min(lim, row);
+        // a 64-column block needs the element predicate when it reaches beyond this key index
+        mask_from = it.Lk;
+        if (p.causal) mask_from = min(mask_from, it.q0 + 128 * s + 1);
+        c0 = (p.bias ? p.bias[it.b] : p.bias_scalar) * kLog2e;
+        if constexpr (kScoreMod) sm_row = p.score_mod + (int64_t)it.b * p.Tk;
+      }
+
+      for (int j = 0; j < n_mine; ++j) {
+        // jobs are ordered by key tile, query tile 0 before 1: (0,0) (1,0) (0,1) (1,1) ...
+        const int n = jobs_base + (s == 0 ? j + min(j, n1) : j + min(j + 1, n0));
+        const int buf = n % kSBufs;
+        ok = mbar_wait_warp(bar(L::kSFull + buf), (uint32_t)(n / kSBufs) & 1u, abort_flag, kSiteBase + 10 + s);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int hh = 0; hh < kColsMine / 64; ++hh) {
+          const uint32_t s_addr = tmem_lane + kColS + 128 * buf + 64 * (g + hh);
+          const int col0 = j * kTileN + 64 * (g + hh);
+          // the predicate code exists only in the instantiation used by boundary tiles
+          if (col0 + 64 > mask_from)
+            fwd_sigmoid_half_tile<kBF16, kScoreMod, true>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
+          else
+            fwd_sigmoid_half_tile<kBF16, kScoreMod, false>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
+        }
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kPFull + buf));  // 256 arrivals on one barrier would serialise
       }
-    }
+      if (!ok) break;
+      jobs_base += n0 + n1;
 
-    if (n_mine == 0) {
-      // this tile is entirely padding (or beyond Tq): zero rows
-      if (row < p.Tq) {
+      // ---------------------------------------------------------- epilogue of the item
+      const FwdItem it = fwd_decode_item(p, item_ring[slot]);
+      const int row = it.q0 + 128 * s + lane_row;
+      // this thread's output columns (16-bit)
+      uint8_t* o_row = reinterpret_cast<uint8_t*>(p.o) +
+                       2 * ((int64_t)it.b * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)row * p.o_st) + g * D;
+      if (n_mine == 0) {
+        // this tile is entirely padding (or beyond Tq): zero rows
+        if (row < p.Tq) {
 #pragma unroll
-        for (int c = 0; c < kDMine / 8; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
+          for (int c = 0; c < kDMine / 8; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
+        }
       }
-    } else if (ok) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::kOFull), 0, abort_flag, kSiteBase + 12));
-      if (ok) {
+      if (it.n_max > 0) {
+        // Every sigmoid warp waits for the item's last product, also one whose tile had no work:
+        // its arrival below must not run ahead into the barrier phase of the previous item.
+        ok = mbar_wait_warp(bar(L::kOFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 12);
+        if (!ok) break;
+        ++act;
         tc_fence_after_sync();
-        const uint32_t o_addr = tmem + lane_addr + kColO + D * s + g * kDMine;
-        const bool live = row < Lq;
+        // O leaves TMEM already rounded to 16 bits, so that few registers are live across the hand-over
+        uint4 w[kDMine / 32][4];
+        if (n_mine > 0) {
+          const uint32_t o_addr = tmem_lane + kColO + D * s + g * kDMine;
+          const bool live = row < it.Lq;
 #pragma unroll
-        for (int c = 0; c < kDMine / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32_sync(o_addr + c * 32, r);
-          if (row < p.Tq) {
+          for (int c = 0; c < kDMine / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32_sync(o_addr + c * 32, r);
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 w;
-              w.x = pack2<kBF16>(__uint_as_float(r[8 * q4 + 0]), __uint_as_float(r[8 * q4 + 1]));
-              w.y = pack2<kBF16>(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3]));
-              w.z = pack2<kBF16>(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5]));
-              w.w = pack2<kBF16>(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7]));
-              if (!live) w = make_uint4(0, 0, 0, 0);
-              *reinterpret_cast<uint4*>(o_row + 64 * c + 16 * q4) = w;
+              w[c][q4].x = pack2<kBF16>(__uint_as_float(r[8 * q4 + 0]), __uint_as_float(r[8 * q4 + 1]));
+              w[c][q4].y = pack2<kBF16>(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3]));
+              w[c][q4].z = pack2<kBF16>(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5]));
+              w[c][q4].w = pack2<kBF16>(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7]));
+              if (!live) w[c][q4] = make_uint4(0, 0, 0, 0);
             }
           }
         }
+        // O is in registers: the next item's products may overwrite the accumulators
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kOEmpty));
+        if (n_mine > 0 && row < p.Tq) {
+#pragma unroll
+          for (int c = 0; c < kDMine / 32; ++c) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(o_row + 64 * c + 16 * q4) = w[c][q4];
+          }
+        }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(L::kItemEmpty + slot));
     }
   }
 
@@ -578,6 +745,16 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   if (warp == kFwdIssuerWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
+  }
+  if (threadIdx.x == 0) {
+    // the last CTA to finish leaves both counters at zero for the next launch that uses them
+    __threadfence();
+    const unsigned int done = atomicAdd(p.ticket + 1, 1u);
+    if (done == gridDim.x - 1) {
+      p.ticket[0] = 0u;
+      p.ticket[1] = 0u;
+      __threadfence();
+    }
   }
 }
 

@@ -75,6 +75,18 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, site)) != 0;
 }
 
+// ---------------------------------------------------------------- register re-allocation
+// Executed by all four warps of an aligned group of four warps: hands registers back to the SM's
+// pool (dec) or takes more from it (inc; waits until another group has released enough).
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

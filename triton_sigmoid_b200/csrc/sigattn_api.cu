@@ -3,6 +3,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
+#include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <stdio.h>
 #include <string.h>
@@ -121,6 +123,41 @@ int set_smem(K kernel, int bytes) {
   return 0;
 }
 
+// Work-item counters of the persistent forward kernel: a ring of (next item, finished CTAs) pairs.
+// Each launch takes the next pair; the kernel leaves its pair at zero when its last CTA finishes,
+// so a pair is only in doubt if more than kTicketSlots forward launches are in flight at once on
+// one device.
+constexpr int kTicketSlots = 1024;
+__device__ unsigned int g_fwd_tickets[2 * kTicketSlots];
+
+struct FwdDeviceInfo {
+  unsigned int* tickets = nullptr;
+  int n_sm = 0;
+};
+
+// Device address of the counters and the SM count, looked up once per device (which must be current).
+int fwd_device_info(int device, FwdDeviceInfo* out) {
+  constexpr int kMaxDevices = 64;
+  static FwdDeviceInfo cached[kMaxDevices];
+  static std::mutex mu;
+  if (device < 0 || device >= kMaxDevices) return fail(-2, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[device].tickets) {
+    unsigned int* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_fwd_tickets);
+    if (e != cudaSuccess || !ptr)
+      return fail(-100, "cudaGetSymbolAddress(forward item counters) failed on device %d: %s", device,
+                  cudaGetErrorString(e));
+    int n_sm = 0;
+    SIG_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
+    if (n_sm <= 0) return fail(-100, "device %d reports %d multiprocessors", device, n_sm);
+    cached[device].n_sm = n_sm;
+    cached[device].tickets = ptr;
+  }
+  *out = cached[device];
+  return 0;
+}
+
 template <int D, bool kBF16, bool kScoreMod>
 int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm) {
   using namespace sigattn;
@@ -144,7 +181,15 @@ int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   fp.Tk = p->Tk;
   fp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
   fp.n_qblk = (p->Tq + kFwdBlockM - 1) / kFwdBlockM;
-  dim3 grid(fp.n_qblk, p->H, p->B);
+  const int64_t n_items = (int64_t)fp.n_qblk * p->H * p->B;
+  if (n_items > INT32_MAX) return fail(-2, "too many (batch, head, query block) items: %lld", (long long)n_items);
+  fp.n_items = (int)n_items;
+  FwdDeviceInfo info;
+  if (int rc = fwd_device_info(p->device, &info)) return rc;
+  static std::atomic<unsigned int> next_slot[64];
+  fp.ticket = info.tickets + 2 * (next_slot[p->device].fetch_add(1u) % kTicketSlots);
+  // persistent: one CTA per SM (the kernel's shared memory allows no more), fewer when there are fewer items
+  dim3 grid((unsigned int)std::min<int64_t>(n_items, info.n_sm));
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   if (p->ev_main_start) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream));
   kernel<<<grid, kFwdThreads, smem, stream>>>(qm, km, vm, fp);
