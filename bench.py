@@ -42,13 +42,15 @@ sys.path.insert(0, ROOT)
 
 WORKLOADS = {
     # name: B, N, H, D, dtype, causal, padded, std, seed
+    # cfg1 is the reference's CPU-runnable case (float32: the exact FMA-pipe kernels, not the tensor-core ones)
+    "cfg1": dict(B=2, N=256, H=4, D=64, dtype="fp32", causal=False, padded=False, std=1.0, seed=0),
     "cfg2": dict(B=4, N=4096, H=16, D=64, dtype="fp16", causal=False, padded=False, std=1.0, seed=1),
     "cfg2-causal": dict(B=4, N=4096, H=16, D=64, dtype="fp16", causal=True, padded=False, std=1.0, seed=1),
     "cfg3": dict(B=16, N=2048, H=8, D=64, dtype="bf16", causal=False, padded=True, lo=256, std=1.0, seed=2),
     "cfg3-causal": dict(B=16, N=2048, H=8, D=64, dtype="bf16", causal=True, padded=True, lo=256, std=1.0, seed=2),
     "cfg4": dict(B=8, N=8192, H=32, D=128, dtype="bf16", causal=True, padded=False, std=0.5, seed=3, strong=True),
 }
-DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16}
+DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}
 
 
 def parse_workload(name: str) -> dict:

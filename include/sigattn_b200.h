@@ -16,7 +16,7 @@
  *    must be 16-byte aligned and every stride times the element size a multiple of 16 bytes.
  *  - Return value 0 = launched; negative = rejected before any launch, with a message
  *    available from sigattn_last_error() on the calling thread.
- *  - Supported: dtype fp16 / bf16, D in {64, 128}, 1 <= H, B, Tq, Tk (zero-sized problems
+ *  - Supported: dtype fp16 / bf16 / fp32, D in {64, 128}, 1 <= H, B, Tq, Tk (zero-sized problems
  *    return 0 without launching).
  */
 #ifndef SIGATTN_B200_H_
@@ -31,7 +31,10 @@ extern "C" {
 
 #define SIGATTN_ABI_VERSION 1
 
-enum SigAttnDtype { SIGATTN_FP16 = 0, SIGATTN_BF16 = 1 };
+/* fp16 / bf16: tensor-core kernels.  fp32: exact single-precision kernels on the FMA pipe (the
+ * reference accepts float32, src/triton_sigmoid/__init__.py:48, and tests it to 1e-5); they need no
+ * workspace, and base pointers / strides must be multiples of 16 bytes as for the other types. */
+enum SigAttnDtype { SIGATTN_FP16 = 0, SIGATTN_BF16 = 1, SIGATTN_FP32 = 2 };
 
 enum SigAttnFlags {
   SIGATTN_CAUSAL = 1u << 0, /* key j visible to query i only if j <= i */

@@ -56,9 +56,14 @@ def test_seq_lens_shape():
         m.sigmoid_attention_padded(q, k, v, seq_lens_q=torch.zeros(2, 1, dtype=torch.int32))
 
 
-def test_float32_is_refused_not_downcast():
+def test_float32_is_accepted_and_other_dtypes_are_refused():
+    """float32 is a supported dtype (exact kernels), so on CPU tensors it gets as far as the
+    device check; float64 is refused outright, never downcast."""
     q, k, v = _qkv(dtype=torch.float32)
-    with pytest.raises(NotImplementedError, match="float32"):
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        m.sigmoid_attention(q, k, v)
+    q, k, v = _qkv(dtype=torch.float64)
+    with pytest.raises(NotImplementedError, match="float64"):
         m.sigmoid_attention(q, k, v)
 
 

@@ -14,6 +14,7 @@ from ._paths import LIB_PATH
 
 SIGATTN_FP16 = 0
 SIGATTN_BF16 = 1
+SIGATTN_FP32 = 2
 SIGATTN_CAUSAL = 1
 SIGATTN_STATIC_SCRATCH_ELEMS = 8 * 1024 * 1024
 

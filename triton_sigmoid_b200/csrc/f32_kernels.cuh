@@ -1,0 +1,322 @@
+// fp32 path: the same forward and backward for float32 tensors, in IEEE single precision on the
+// FMA pipe.
+//
+// The reference accepts float32 (src/triton_sigmoid/__init__.py:48) and its tests hold that
+// dtype to 1e-5 (tests/conftest.py:27-34), which a tf32 tensor-core product (10-bit mantissa)
+// cannot meet; the 16-bit tcgen05 kernels are the fast path, this one is the exact path.  The
+// work is split as in the reference: one forward kernel, a dK/dV kernel that walks the query
+// tiles of one key tile and a dQ kernel that walks the key tiles of one query tile
+// (src/triton_sigmoid/sigmoid_triton_dense.py:23-154, 162-467), so nothing is accumulated
+// across CTAs and the results are run-to-run deterministic.
+//
+// Tiles are 64 x 64; 256 threads as a 16 x 16 grid, thread (ty, tx) owning rows ty + 16 a and
+// columns tx + 16 c of every product (a stride of 16 keeps the shared-memory reads of a warp on
+// distinct banks).  Rows beyond a valid length are zero in shared memory whatever global memory
+// holds, masked probabilities are exactly zero.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sigattn {
+
+struct F32Params {
+  const float *q, *k, *v, *dout;
+  float *o, *dq, *dk, *dv;
+  // element strides: batch, token, head
+  int64_t q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, o_sb, o_st, o_sh;
+  int64_t do_sb, do_st, do_sh, dq_sb, dq_st, dq_sh, dk_sb, dk_st, dk_sh, dv_sb, dv_st, dv_sh;
+  const int* lens_q;
+  const int* lens_k;
+  const float* bias;       // [B] or nullptr
+  const float* score_mod;  // [B, Tk] or nullptr
+  float scale;
+  float bias_scalar;
+  int B, H, Tq, Tk;
+  int causal;
+};
+
+constexpr int kF32Tile = 64;
+constexpr int kF32Threads = 256;
+
+template <int D>
+struct F32Smem {
+  static constexpr int kRow = D + 4;             // floats per tile row (padding keeps float4 reads conflict-free)
+  static constexpr int kTileFloats = kF32Tile * kRow;
+  static constexpr int kPRow = kF32Tile + 1;
+  static constexpr int kPFloats = kF32Tile * kPRow;
+  static constexpr int kFwdBytes = (3 * kTileFloats + kPFloats) * 4;        // Q K V | P
+  static constexpr int kDkdvBytes = (4 * kTileFloats + 2 * kPFloats) * 4;   // K V Q dO | P dS
+  static constexpr int kDqBytes = (4 * kTileFloats + kPFloats) * 4;         // Q dO K V | dS
+};
+
+// Rows [row0, row0 + 64) of a (token, head-dim) slab into shared memory; rows at or beyond `limit` are zero.
+template <int D>
+__device__ __forceinline__ void f32_load_tile(float* dst, const float* src, int64_t stride_t, int row0, int limit) {
+  constexpr int kRow = F32Smem<D>::kRow;
+  for (int i = threadIdx.x; i < kF32Tile * (D / 4); i += kF32Threads) {
+    const int r = i / (D / 4), c = i % (D / 4);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row0 + r < limit) v = *reinterpret_cast<const float4*>(src + (int64_t)(row0 + r) * stride_t + 4 * c);
+    *reinterpret_cast<float4*>(dst + r * kRow + 4 * c) = v;
+  }
+}
+
+// acc[a][c] = sum_d A[ty + 16 a][d] * B[tx + 16 c][d]   (both tiles row-major over d)
+template <int D>
+__device__ __forceinline__ void f32_dot_rows(const float* A, const float* Bt, int ty, int tx, float (&acc)[4][4]) {
+  constexpr int kRow = F32Smem<D>::kRow;
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
+#pragma unroll 4
+  for (int d = 0; d < D; d += 4) {
+    float4 av[4], bv[4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) av[a] = *reinterpret_cast<const float4*>(A + (ty + 16 * a) * kRow + d);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) bv[c] = *reinterpret_cast<const float4*>(Bt + (tx + 16 * c) * kRow + d);
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        acc[a][c] = fmaf(av[a].x, bv[c].x, acc[a][c]);
+        acc[a][c] = fmaf(av[a].y, bv[c].y, acc[a][c]);
+        acc[a][c] = fmaf(av[a].z, bv[c].z, acc[a][c]);
+        acc[a][c] = fmaf(av[a].w, bv[c].w, acc[a][c]);
+      }
+  }
+}
+
+// acc[a][c] += sum_j W[j-or-row index] * X[j][tx + 16 c]:
+// kTransposed = false: W row-major [row][j], rows ty + 16 a     (O += P V,  dQ += dS K)
+// kTransposed = true : W row-major [j][col], columns ty + 16 a  (dV += P^T dO, dK += dS^T Q)
+template <int D, bool kTransposed>
+__device__ __forceinline__ void f32_accumulate(const float* W, const float* X, int ty, int tx, float (&acc)[4][D / 16]) {
+  constexpr int kRow = F32Smem<D>::kRow;
+  constexpr int kPRow = F32Smem<D>::kPRow;
+#pragma unroll 4
+  for (int j = 0; j < kF32Tile; ++j) {
+    float w[4], x[D / 16];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) w[a] = kTransposed ? W[j * kPRow + ty + 16 * a] : W[(ty + 16 * a) * kPRow + j];
+#pragma unroll
+    for (int c = 0; c < D / 16; ++c) x[c] = X[j * kRow + tx + 16 * c];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int c = 0; c < D / 16; ++c) acc[a][c] = fmaf(w[a], x[c], acc[a][c]);
+  }
+}
+
+__device__ __forceinline__ float f32_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+struct F32Item {
+  int b, h, Lq, Lk;
+};
+__device__ __forceinline__ F32Item f32_item(const F32Params& p) {
+  F32Item it;
+  it.h = blockIdx.y;
+  it.b = blockIdx.z;
+  it.Lq = p.Tq;
+  it.Lk = p.Tk;
+  if (p.lens_q) it.Lq = min(max(p.lens_q[it.b], 0), p.Tq);
+  if (p.lens_k) it.Lk = min(max(p.lens_k[it.b], 0), p.Tk);
+  return it;
+}
+
+// ---------------------------------------------------------------- forward
+template <int D>
+__global__ void __launch_bounds__(kF32Threads) sigattn_fwd_f32_kernel(const F32Params p) {
+  using L = F32Smem<D>;
+  extern __shared__ float4 f32_smem4[];
+  float* Qs = reinterpret_cast<float*>(f32_smem4);
+  float* Ks = Qs + L::kTileFloats;
+  float* Vs = Ks + L::kTileFloats;
+  float* Ps = Vs + L::kTileFloats;
+  const F32Item it = f32_item(p);
+  const int q0 = blockIdx.x * kF32Tile;
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const float* qb = p.q + (int64_t)it.b * p.q_sb + (int64_t)it.h * p.q_sh;
+  const float* kb = p.k + (int64_t)it.b * p.k_sb + (int64_t)it.h * p.k_sh;
+  const float* vb = p.v + (int64_t)it.b * p.v_sb + (int64_t)it.h * p.v_sh;
+  const float bias = p.bias ? p.bias[it.b] : p.bias_scalar;
+  const float* sm = p.score_mod ? p.score_mod + (int64_t)it.b * p.Tk : nullptr;
+
+  float o[4][D / 16];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int c = 0; c < D / 16; ++c) o[a][c] = 0.f;
+
+  int kv_end = (q0 < it.Lq) ? it.Lk : 0;
+  if (p.causal) kv_end = min(kv_end, q0 + kF32Tile);
+  if (kv_end > 0) f32_load_tile<D>(Qs, qb, p.q_st, q0, it.Lq);
+  for (int k0 = 0; k0 < kv_end; k0 += kF32Tile) {
+    __syncthreads();  // the previous tile's K, V and P are no longer read
+    f32_load_tile<D>(Ks, kb, p.k_st, k0, it.Lk);
+    f32_load_tile<D>(Vs, vb, p.v_st, k0, it.Lk);
+    __syncthreads();
+    float s[4][4];
+    f32_dot_rows<D>(Qs, Ks, ty, tx, s);
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int i = q0 + ty + 16 * a, j = k0 + tx + 16 * c;
+        const bool visible = i < it.Lq && j < it.Lk && (!p.causal || j <= i);
+        float x = s[a][c] * p.scale + bias;
+        if (sm && j < p.Tk) x += sm[j];
+        Ps[(ty + 16 * a) * L::kPRow + tx + 16 * c] = visible ? f32_sigmoid(x) : 0.f;
+      }
+    __syncthreads();
+    f32_accumulate<D, false>(Ps, Vs, ty, tx, o);
+  }
+  float* ob = p.o + (int64_t)it.b * p.o_sb + (int64_t)it.h * p.o_sh;
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int i = q0 + ty + 16 * a;
+    if (i < p.Tq) {
+#pragma unroll
+      for (int c = 0; c < D / 16; ++c) ob[(int64_t)i * p.o_st + tx + 16 * c] = (i < it.Lq) ? o[a][c] : 0.f;
+    }
+  }
+}
+
+// P and dS of one 64 x 64 tile pair into shared memory (rows = queries, columns = keys).
+// Qs, dOs: query tile; Ks, Vs: key tile.  Ps may be nullptr when only dS is wanted.
+template <int D>
+__device__ __forceinline__ void f32_p_and_ds(const F32Params& p, const F32Item& it, const float* Qs, const float* dOs,
+                                             const float* Ks, const float* Vs, float* Ps, float* dSs, int q0, int k0,
+                                             float bias, const float* sm, int ty, int tx) {
+  using L = F32Smem<D>;
+  float s[4][4], dp[4][4];
+  f32_dot_rows<D>(Qs, Ks, ty, tx, s);
+  f32_dot_rows<D>(dOs, Vs, ty, tx, dp);
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int i = q0 + ty + 16 * a, j = k0 + tx + 16 * c;
+      const bool visible = i < it.Lq && j < it.Lk && (!p.causal || j <= i);
+      float x = s[a][c] * p.scale + bias;
+      if (sm && j < p.Tk) x += sm[j];
+      const float pr = visible ? f32_sigmoid(x) : 0.f;
+      if (Ps) Ps[(ty + 16 * a) * L::kPRow + tx + 16 * c] = pr;
+      dSs[(ty + 16 * a) * L::kPRow + tx + 16 * c] = visible ? pr * (1.0f - pr) * dp[a][c] : 0.f;
+    }
+}
+
+// ---------------------------------------------------------------- backward: dK, dV of one key tile
+template <int D>
+__global__ void __launch_bounds__(kF32Threads) sigattn_bwd_dkdv_f32_kernel(const F32Params p) {
+  using L = F32Smem<D>;
+  extern __shared__ float4 f32_smem4[];
+  float* Ks = reinterpret_cast<float*>(f32_smem4);
+  float* Vs = Ks + L::kTileFloats;
+  float* Qs = Vs + L::kTileFloats;
+  float* dOs = Qs + L::kTileFloats;
+  float* Ps = dOs + L::kTileFloats;
+  float* dSs = Ps + L::kPFloats;
+  const F32Item it = f32_item(p);
+  const int k0 = blockIdx.x * kF32Tile;
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const float* qb = p.q + (int64_t)it.b * p.q_sb + (int64_t)it.h * p.q_sh;
+  const float* kb = p.k + (int64_t)it.b * p.k_sb + (int64_t)it.h * p.k_sh;
+  const float* vb = p.v + (int64_t)it.b * p.v_sb + (int64_t)it.h * p.v_sh;
+  const float* dob = p.dout + (int64_t)it.b * p.do_sb + (int64_t)it.h * p.do_sh;
+  const float bias = p.bias ? p.bias[it.b] : p.bias_scalar;
+  const float* sm = p.score_mod ? p.score_mod + (int64_t)it.b * p.Tk : nullptr;
+
+  float dk[4][D / 16], dv[4][D / 16];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int c = 0; c < D / 16; ++c) dk[a][c] = dv[a][c] = 0.f;
+
+  const int q_end = (k0 < it.Lk) ? it.Lq : 0;
+  const int q_begin = p.causal ? (k0 / kF32Tile) * kF32Tile : 0;  // earlier query tiles see none of these keys
+  if (q_begin < q_end) {
+    f32_load_tile<D>(Ks, kb, p.k_st, k0, it.Lk);
+    f32_load_tile<D>(Vs, vb, p.v_st, k0, it.Lk);
+  }
+  for (int q0 = q_begin; q0 < q_end; q0 += kF32Tile) {
+    __syncthreads();
+    f32_load_tile<D>(Qs, qb, p.q_st, q0, it.Lq);
+    f32_load_tile<D>(dOs, dob, p.do_st, q0, it.Lq);
+    __syncthreads();
+    f32_p_and_ds<D>(p, it, Qs, dOs, Ks, Vs, Ps, dSs, q0, k0, bias, sm, ty, tx);
+    __syncthreads();
+    f32_accumulate<D, true>(Ps, dOs, ty, tx, dv);
+    f32_accumulate<D, true>(dSs, Qs, ty, tx, dk);
+  }
+  float* dkb = p.dk + (int64_t)it.b * p.dk_sb + (int64_t)it.h * p.dk_sh;
+  float* dvb = p.dv + (int64_t)it.b * p.dv_sb + (int64_t)it.h * p.dv_sh;
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int j = k0 + ty + 16 * a;
+    if (j < p.Tk) {
+      const bool live = j < it.Lk;
+#pragma unroll
+      for (int c = 0; c < D / 16; ++c) {
+        dkb[(int64_t)j * p.dk_st + tx + 16 * c] = live ? dk[a][c] * p.scale : 0.f;
+        dvb[(int64_t)j * p.dv_st + tx + 16 * c] = live ? dv[a][c] : 0.f;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- backward: dQ of one query tile
+template <int D>
+__global__ void __launch_bounds__(kF32Threads) sigattn_bwd_dq_f32_kernel(const F32Params p) {
+  using L = F32Smem<D>;
+  extern __shared__ float4 f32_smem4[];
+  float* Qs = reinterpret_cast<float*>(f32_smem4);
+  float* dOs = Qs + L::kTileFloats;
+  float* Ks = dOs + L::kTileFloats;
+  float* Vs = Ks + L::kTileFloats;
+  float* dSs = Vs + L::kTileFloats;
+  const F32Item it = f32_item(p);
+  const int q0 = blockIdx.x * kF32Tile;
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const float* qb = p.q + (int64_t)it.b * p.q_sb + (int64_t)it.h * p.q_sh;
+  const float* kb = p.k + (int64_t)it.b * p.k_sb + (int64_t)it.h * p.k_sh;
+  const float* vb = p.v + (int64_t)it.b * p.v_sb + (int64_t)it.h * p.v_sh;
+  const float* dob = p.dout + (int64_t)it.b * p.do_sb + (int64_t)it.h * p.do_sh;
+  const float bias = p.bias ? p.bias[it.b] : p.bias_scalar;
+  const float* sm = p.score_mod ? p.score_mod + (int64_t)it.b * p.Tk : nullptr;
+
+  float dq[4][D / 16];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int c = 0; c < D / 16; ++c) dq[a][c] = 0.f;
+
+  int kv_end = (q0 < it.Lq) ? it.Lk : 0;
+  if (p.causal) kv_end = min(kv_end, q0 + kF32Tile);
+  if (kv_end > 0) {
+    f32_load_tile<D>(Qs, qb, p.q_st, q0, it.Lq);
+    f32_load_tile<D>(dOs, dob, p.do_st, q0, it.Lq);
+  }
+  for (int k0 = 0; k0 < kv_end; k0 += kF32Tile) {
+    __syncthreads();
+    f32_load_tile<D>(Ks, kb, p.k_st, k0, it.Lk);
+    f32_load_tile<D>(Vs, vb, p.v_st, k0, it.Lk);
+    __syncthreads();
+    f32_p_and_ds<D>(p, it, Qs, dOs, Ks, Vs, nullptr, dSs, q0, k0, bias, sm, ty, tx);
+    __syncthreads();
+    f32_accumulate<D, false>(dSs, Ks, ty, tx, dq);
+  }
+  float* dqb = p.dq + (int64_t)it.b * p.dq_sb + (int64_t)it.h * p.dq_sh;
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int i = q0 + ty + 16 * a;
+    if (i < p.Tq) {
+#pragma unroll
+      for (int c = 0; c < D / 16; ++c) dqb[(int64_t)i * p.dq_st + tx + 16 * c] = (i < it.Lq) ? dq[a][c] * p.scale : 0.f;
+    }
+  }
+}
+
+}  // namespace sigattn

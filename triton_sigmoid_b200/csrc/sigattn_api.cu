@@ -11,6 +11,7 @@
 
 #include "../../include/sigattn_b200.h"
 #include "bwd_kernel.cuh"
+#include "f32_kernels.cuh"
 #include "fwd_kernel.cuh"
 
 namespace {
@@ -76,7 +77,8 @@ int check_common(const SigAttnParams* p, bool backward) {
   if (p->struct_bytes != sizeof(SigAttnParams))
     return fail(-1, "struct_bytes %u != sizeof(SigAttnParams) %zu (ABI mismatch)", p->struct_bytes,
                 sizeof(SigAttnParams));
-  if (p->dtype != SIGATTN_FP16 && p->dtype != SIGATTN_BF16) return fail(-2, "unsupported dtype %d (fp16=0, bf16=1)", p->dtype);
+  if (p->dtype != SIGATTN_FP16 && p->dtype != SIGATTN_BF16 && p->dtype != SIGATTN_FP32)
+    return fail(-2, "unsupported dtype %d (fp16=0, bf16=1, fp32=2)", p->dtype);
   if (p->D != 64 && p->D != 128) return fail(-2, "unsupported head dimension %d (64 or 128)", p->D);
   if (p->B < 0 || p->H < 0 || p->Tq < 0 || p->Tk < 0) return fail(-2, "negative extent");
   if (p->H > 65535 || p->B > 65535) return fail(-2, "B and H must not exceed 65535");
@@ -91,11 +93,12 @@ bool is_contiguous(const int64_t* s, int T, int H, int D) {
   return s[2] == D && s[1] == (int64_t)H * D && s[0] == (int64_t)T * H * D;
 }
 
-// Zero-fill a (B,T,H,D) 16-bit tensor; only used for degenerate problems (no keys / no queries).
-int zero_fill(void* ptr, const int64_t* strides, int B, int T, int H, int D, cudaStream_t stream, const char* name) {
+// Zero-fill a (B,T,H,D) tensor; only used for degenerate problems (no keys / no queries).
+int zero_fill(void* ptr, const int64_t* strides, int B, int T, int H, int D, int dtype, cudaStream_t stream,
+              const char* name) {
   if (T == 0) return 0;
   if (!is_contiguous(strides, T, H, D)) return fail(-2, "%s: an empty problem needs a contiguous output", name);
-  SIG_CUDA(cudaMemsetAsync(ptr, 0, (size_t)B * T * H * D * 2, stream));
+  SIG_CUDA(cudaMemsetAsync(ptr, 0, (size_t)B * T * H * D * (dtype == SIGATTN_FP32 ? 4 : 2), stream));
   return 0;
 }
 
@@ -279,6 +282,74 @@ int static_scratch_ptr(int device, float** out) {
   return 0;
 }
 
+// float32 tensors: the exact FMA-pipe kernels (no tensor maps, no workspace).
+template <int D>
+int launch_f32_d(const SigAttnParams* p, bool backward) {
+  using namespace sigattn;
+  F32Params fp = {};
+  fp.q = static_cast<const float*>(p->q);
+  fp.k = static_cast<const float*>(p->k);
+  fp.v = static_cast<const float*>(p->v);
+  fp.dout = static_cast<const float*>(p->dout);
+  fp.o = static_cast<float*>(p->o);
+  fp.dq = static_cast<float*>(p->dq);
+  fp.dk = static_cast<float*>(p->dk);
+  fp.dv = static_cast<float*>(p->dv);
+  fp.q_sb = p->q_strides[0]; fp.q_st = p->q_strides[1]; fp.q_sh = p->q_strides[2];
+  fp.k_sb = p->k_strides[0]; fp.k_st = p->k_strides[1]; fp.k_sh = p->k_strides[2];
+  fp.v_sb = p->v_strides[0]; fp.v_st = p->v_strides[1]; fp.v_sh = p->v_strides[2];
+  fp.o_sb = p->o_strides[0]; fp.o_st = p->o_strides[1]; fp.o_sh = p->o_strides[2];
+  fp.do_sb = p->do_strides[0]; fp.do_st = p->do_strides[1]; fp.do_sh = p->do_strides[2];
+  fp.dq_sb = p->dq_strides[0]; fp.dq_st = p->dq_strides[1]; fp.dq_sh = p->dq_strides[2];
+  fp.dk_sb = p->dk_strides[0]; fp.dk_st = p->dk_strides[1]; fp.dk_sh = p->dk_strides[2];
+  fp.dv_sb = p->dv_strides[0]; fp.dv_st = p->dv_strides[1]; fp.dv_sh = p->dv_strides[2];
+  fp.lens_q = p->seq_lens_q;
+  fp.lens_k = p->seq_lens_k;
+  fp.bias = p->bias;
+  fp.score_mod = p->score_mod;
+  fp.scale = p->scale;
+  fp.bias_scalar = p->bias_scalar;
+  fp.B = p->B; fp.H = p->H; fp.Tq = p->Tq; fp.Tk = p->Tk;
+  fp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  const unsigned int n_q = (unsigned int)((p->Tq + kF32Tile - 1) / kF32Tile);
+  const unsigned int n_k = (unsigned int)((p->Tk + kF32Tile - 1) / kF32Tile);
+  if (p->ev_main_start) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream));
+  if (!backward) {
+    auto kernel = sigattn_fwd_f32_kernel<D>;
+    if (int rc = set_smem(kernel, F32Smem<D>::kFwdBytes)) return rc;
+    kernel<<<dim3(n_q, p->H, p->B), kF32Threads, F32Smem<D>::kFwdBytes, stream>>>(fp);
+    SIG_CUDA(cudaGetLastError());
+  } else {
+    auto kdkdv = sigattn_bwd_dkdv_f32_kernel<D>;
+    auto kdq = sigattn_bwd_dq_f32_kernel<D>;
+    if (int rc = set_smem(kdkdv, F32Smem<D>::kDkdvBytes)) return rc;
+    if (int rc = set_smem(kdq, F32Smem<D>::kDqBytes)) return rc;
+    kdkdv<<<dim3(n_k, p->H, p->B), kF32Threads, F32Smem<D>::kDkdvBytes, stream>>>(fp);
+    SIG_CUDA(cudaGetLastError());
+    kdq<<<dim3(n_q, p->H, p->B), kF32Threads, F32Smem<D>::kDqBytes, stream>>>(fp);
+    SIG_CUDA(cudaGetLastError());
+  }
+  if (p->ev_main_stop) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_stop), stream));
+  return 0;
+}
+
+int launch_f32(const SigAttnParams* p, bool backward) {
+  struct Tensor { const void* ptr; const int64_t* strides; const char* name; };
+  const Tensor fwd_t[] = {{p->q, p->q_strides, "q"}, {p->k, p->k_strides, "k"}, {p->v, p->v_strides, "v"}, {p->o, p->o_strides, "o"}};
+  const Tensor bwd_t[] = {{p->q, p->q_strides, "q"}, {p->k, p->k_strides, "k"}, {p->v, p->v_strides, "v"},
+                          {p->dout, p->do_strides, "dout"}, {p->dq, p->dq_strides, "dq"}, {p->dk, p->dk_strides, "dk"},
+                          {p->dv, p->dv_strides, "dv"}};
+  const Tensor* ts = backward ? bwd_t : fwd_t;
+  const int n = backward ? 7 : 4;
+  for (int t = 0; t < n; ++t) {
+    if ((reinterpret_cast<uintptr_t>(ts[t].ptr) & 15u) != 0) return fail(-3, "%s: base pointer must be 16-byte aligned", ts[t].name);
+    for (int i = 0; i < 3; ++i)
+      if (ts[t].strides[i] % 4 != 0) return fail(-3, "%s: strides must be multiples of 4 elements (16 bytes)", ts[t].name);
+  }
+  return p->D == 64 ? launch_f32_d<64>(p, backward) : launch_f32_d<128>(p, backward);
+}
+
 }  // namespace
 
 extern "C" {
@@ -323,7 +394,8 @@ int sigattn_fwd(const SigAttnParams* p) {
   SIG_CUDA(g.enter(p->device));
   if (p->Tq == 0) return 0;
   if (p->Tk == 0)  // no keys at all: the output is all zeros
-    return zero_fill(p->o, p->o_strides, p->B, p->Tq, p->H, p->D, static_cast<cudaStream_t>(p->stream), "o");
+    return zero_fill(p->o, p->o_strides, p->B, p->Tq, p->H, p->D, p->dtype, static_cast<cudaStream_t>(p->stream), "o");
+  if (p->dtype == SIGATTN_FP32) return launch_f32(p, false);
   CUtensorMap qm, km, vm;
   if ((rc = make_map(&qm, p->q, p->dtype, p->B, p->Tq, p->H, p->D, p->q_strides, 128, "q"))) return rc;
   if ((rc = make_map(&km, p->k, p->dtype, p->B, p->Tk, p->H, p->D, p->k_strides, 128, "k"))) return rc;
@@ -356,10 +428,11 @@ int sigattn_bwd(const SigAttnParams* p) {
   if (p->Tq == 0 || p->Tk == 0) {
     // no query or no key: every gradient is zero
     cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
-    if ((rc = zero_fill(p->dq, p->dq_strides, p->B, p->Tq, p->H, p->D, stream, "dq"))) return rc;
-    if ((rc = zero_fill(p->dk, p->dk_strides, p->B, p->Tk, p->H, p->D, stream, "dk"))) return rc;
-    return zero_fill(p->dv, p->dv_strides, p->B, p->Tk, p->H, p->D, stream, "dv");
+    if ((rc = zero_fill(p->dq, p->dq_strides, p->B, p->Tq, p->H, p->D, p->dtype, stream, "dq"))) return rc;
+    if ((rc = zero_fill(p->dk, p->dk_strides, p->B, p->Tk, p->H, p->D, p->dtype, stream, "dk"))) return rc;
+    return zero_fill(p->dv, p->dv_strides, p->B, p->Tk, p->H, p->D, p->dtype, stream, "dv");
   }
+  if (p->dtype == SIGATTN_FP32) return launch_f32(p, true);
   CUtensorMap qm, km, vm, dom;
   if ((rc = make_map(&qm, p->q, p->dtype, p->B, p->Tq, p->H, p->D, p->q_strides, 128, "q"))) return rc;
   if ((rc = make_map(&km, p->k, p->dtype, p->B, p->Tk, p->H, p->D, p->k_strides, 128, "k"))) return rc;

@@ -22,7 +22,8 @@ import torch.nn.functional as F
 from . import _cabi
 
 _NS = "sigattn_b200"
-_SUPPORTED_DTYPES = (torch.float16, torch.bfloat16)
+_SUPPORTED_DTYPES = (torch.float16, torch.bfloat16, torch.float32)
+_DTYPE_CODE = {torch.float16: _cabi.SIGATTN_FP16, torch.bfloat16: _cabi.SIGATTN_BF16, torch.float32: _cabi.SIGATTN_FP32}
 _DEVICE_OK: dict = {}
 
 
@@ -52,7 +53,7 @@ def _base_params(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_cau
     B, Tq, H, D = q.shape
     p = _cabi.SigAttnParams()
     p.struct_bytes = ctypes.sizeof(_cabi.SigAttnParams)
-    p.dtype = _cabi.SIGATTN_BF16 if q.dtype == torch.bfloat16 else _cabi.SIGATTN_FP16
+    p.dtype = _DTYPE_CODE[q.dtype]
     p.B, p.H, p.D, p.Tq, p.Tk = B, H, D, Tq, k.shape[1]
     p.flags = _cabi.SIGATTN_CAUSAL if is_causal else 0
     p.scale = float(scale)
@@ -83,7 +84,7 @@ def _check_kernel_inputs(q, k, v):
     _require_b200(q.device)
     if q.dtype not in _SUPPORTED_DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
         raise NotImplementedError(
-            f"triton_sigmoid_b200 kernels take float16 or bfloat16 q/k/v of one dtype, got "
+            f"triton_sigmoid_b200 kernels take float16, bfloat16 or float32 q/k/v of one dtype, got "
             f"{q.dtype}, {k.dtype}, {v.dtype}"
         )
     if q.shape[-1] not in (64, 128):
@@ -245,13 +246,10 @@ def _pad_head_dim(x: torch.Tensor, D_kernel: int) -> torch.Tensor:
 
 
 def _check_dtype(query, key, value):
-    if query.dtype == torch.float32:
-        raise NotImplementedError(
-            "float32 inputs are not supported by the sm_100a kernels (16-bit tensor-core inputs only); "
-            "cast to float16 or bfloat16"
-        )
+    """float16 / bfloat16 run on the tensor cores; float32 runs the exact single-precision
+    kernels (slower by design: the reference holds float32 to 1e-5, which tf32 cannot meet)."""
     if query.dtype not in _SUPPORTED_DTYPES:
-        raise NotImplementedError(f"unsupported dtype {query.dtype}: use float16 or bfloat16")
+        raise NotImplementedError(f"unsupported dtype {query.dtype}: use float16, bfloat16 or float32")
     if key.dtype != query.dtype or value.dtype != query.dtype:
         raise ValueError(f"query, key and value must share one dtype, got {query.dtype}, {key.dtype}, {value.dtype}")
 
