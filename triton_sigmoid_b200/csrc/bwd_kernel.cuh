@@ -1,5 +1,8 @@
-// Backward kernel: one CTA owns one (batch, head, 128-key tile), keeps K_j and V_j in shared
-// memory and dK_j, dV_j in TMEM, and streams the query tiles Q_i, dO_i past them.
+// Backward kernel.  A work item is one (batch, head, 128-key tile): its K_j and V_j stay in shared
+// memory, dK_j and dV_j in TMEM, and the query tiles Q_i, dO_i are streamed past them.  The kernel
+// is persistent: one CTA per SM takes items from a ticket counter until none are left, so that
+// the loads and first products of the next item overlap the dK/dV epilogue of the current one and
+// uneven items (causal, ragged lengths) balance themselves.
 //
 // Takes over the work of the reference's _bwd_dense_dq_kernel / _bwd_dense_dkdv_kernel
 // (src/triton_sigmoid/sigmoid_triton_dense.py:162-467) and the padded pair
@@ -30,7 +33,7 @@
 // Warp roles (20 warps):
 //   warps 0-15  compute: warp w owns TMEM lanes (key rows) 32 (w & 3) .. +31 and the query
 //               columns 32 (w >> 2) .. +31 of every tile; the same warps drain dQ
-//   warp  16    TMA producer (also clears padded rows of tiles that straddle a valid length)
+//   warp  16    item scheduler + TMA producer (also clears padded rows of tiles that straddle a valid length)
 //   warp  17    tcgen05 issuer A: S^T and dP^T; owns the TMEM allocation
 //   warp  18    tcgen05 issuer B: dV, dK, dQ
 //   warp  19    idle
@@ -59,7 +62,11 @@ struct BwdParams {
   float bias_scalar;
   int B, H, Tq, Tk;
   int causal;
-  int n_kvblk;
+  int n_kvblk;  // ceil(Tk / 128)
+  int n_items;  // B * H * n_kvblk
+  // two counters, zero between launches: [0] items handed out beyond the first per CTA,
+  // [1] CTAs that have finished (the last one clears both)
+  unsigned int* ticket;
 };
 
 constexpr int kBwdComputeWarps = 16;
@@ -103,8 +110,12 @@ struct BwdSmem {
   static constexpr int kDkvFull = kDqEmpty + 2;       // every MMA of the CTA complete
   static constexpr int kKvFix = kDkvFull + 1;         // padded rows of K_j zeroed
   static constexpr int kQdoFix = kKvFix + 1;          // padded rows of the last Q_i / dO_i zeroed
-  static constexpr int kNumBars = kQdoFix + 1;
-  static constexpr int kMiscOff = kBarOff + 8 * kNumBars;
+  static constexpr int kKvEmpty = kQdoFix + 1;        // both issuers: every product that reads K_j / V_j is complete
+  static constexpr int kDkvEmpty = kKvEmpty + 1;      // dK_j, dV_j read out of TMEM (16 warps)
+  static constexpr int kItemFull = kDkvEmpty + 1;     // [2] item index published
+  static constexpr int kItemEmpty = kItemFull + 2;    // [2] item index read by every consumer warp
+  static constexpr int kNumBars = kItemEmpty + 2;
+  static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int), item ring (2 int)
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynBytes = kTotal + 1024;
 };
@@ -178,6 +189,33 @@ __device__ __forceinline__ void bwd_phase_b(uint32_t dp_addr, uint32_t ds_line, 
   }
 }
 
+// One work item, decoded the same way by every warp role.
+struct BwdItem {
+  int b, h, kv0;
+  int Lq, Lk;
+  int i_begin, n_q;     // first query tile that sees this key tile, number of query tiles
+  bool ragged_kv;       // the key tile straddles Lk
+  bool ragged_last_q;   // the last query tile straddles Lq
+};
+__device__ __forceinline__ BwdItem bwd_decode_item(const BwdParams& p, int item) {
+  BwdItem it;
+  const int bh = item / p.n_kvblk;
+  const int j = item - bh * p.n_kvblk;  // key tile; under a causal mask the early (heavy) ones come first
+  it.b = bh / p.H;
+  it.h = bh - it.b * p.H;
+  it.kv0 = j * kBwdTileKV;
+  it.Lq = p.Tq;
+  it.Lk = p.Tk;
+  if (p.lens_q) it.Lq = min(max(p.lens_q[it.b], 0), p.Tq);
+  if (p.lens_k) it.Lk = min(max(p.lens_k[it.b], 0), p.Tk);
+  const int i_end = (it.Lq + kBwdTileQ - 1) / kBwdTileQ;
+  it.i_begin = p.causal ? j : 0;  // query tiles that can see this key tile (top-left aligned)
+  it.n_q = (it.kv0 < it.Lk) ? max(i_end - it.i_begin, 0) : 0;
+  it.ragged_kv = it.kv0 + kBwdTileKV > it.Lk;
+  it.ragged_last_q = (it.i_begin + it.n_q) * kBwdTileQ > it.Lq;  // only the last query tile can straddle Lq
+  return it;
+}
+
 template <int D, bool kBF16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
@@ -198,12 +236,15 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   constexpr uint32_t kColDv = kTwoS ? 384 : 256;
   constexpr uint32_t kColDk = kColDv + D;
   static_assert(kColDk + D <= kTmemCols, "TMEM budget");
-  // index and parity of the per-S-buffer barriers for tile t
-  auto sbuf = [](int t) -> int { return kTwoS ? (t & 1) : 0; };
-  auto spar = [](int t) -> uint32_t { return kTwoS ? (uint32_t)(t >> 1) & 1u : (uint32_t)t & 1u; };
-  // where dQ (or dQ^T) of tile t is written
-  auto dq_col = [&](int t) -> uint32_t { return kTwoS ? kColS + 128u * (uint32_t)(t & 1) : kColDp; };
+  // Query tiles are numbered through the whole life of the CTA (g = tiles of earlier items + index
+  // within the item): stages, S buffers and barrier parities simply run on from item to item.
+  // index and parity of the per-S-buffer barriers for tile g
+  auto sbuf = [](int g) -> int { return kTwoS ? (g & 1) : 0; };
+  auto spar = [](int g) -> uint32_t { return kTwoS ? (uint32_t)(g >> 1) & 1u : (uint32_t)g & 1u; };
+  // where dQ (or dQ^T) of tile g is written
+  auto dq_col = [&](int g) -> uint32_t { return kTwoS ? kColS + 128u * (uint32_t)(g & 1) : kColDp; };
   constexpr int kSiteBase = 0x20000;
+  constexpr int kItemReaders = kBwdComputeWarps + 2;  // compute warps and the two issuing warps
 
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -212,39 +253,10 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   auto bar = [&](int slot) -> uint32_t { return bars + 8u * slot; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
+  volatile int* item_ring = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 8);  // [2]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-
-  // ---------------------------------------------------------------- work item
-  const int j = blockIdx.x;  // key tile
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
-  const int kv0 = j * kBwdTileKV;
-  int Lq = p.Tq, Lk = p.Tk;
-  if (p.lens_q) Lq = min(max(p.lens_q[b], 0), p.Tq);
-  if (p.lens_k) Lk = min(max(p.lens_k[b], 0), p.Tk);
-  const int i_end = (Lq + kBwdTileQ - 1) / kBwdTileQ;
-  const int i_begin = p.causal ? j : 0;  // query tiles that can see this key tile (top-left aligned)
-  const int n_q = (kv0 < Lk) ? max(i_end - i_begin, 0) : 0;
-  const bool ragged_kv = kv0 + kBwdTileKV > Lk;
-  // only the last query tile can straddle Lq
-  const bool ragged_last_q = (i_begin + n_q) * kBwdTileQ > Lq;
-
-  uint8_t* dk_base = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((int64_t)b * p.dk_sb + (int64_t)h * p.dk_sh);
-  uint8_t* dv_base = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((int64_t)b * p.dv_sb + (int64_t)h * p.dv_sh);
-
-  if (n_q == 0) {
-    constexpr int kChunksPerRow = D * 2 / 16;
-    for (int i = threadIdx.x; i < kBwdTileKV * kChunksPerRow; i += kBwdThreads) {
-      const int row = kv0 + i / kChunksPerRow;
-      if (row < p.Tk) {
-        *reinterpret_cast<uint4*>(dk_base + 2 * (int64_t)row * p.dk_st + 16 * (i % kChunksPerRow)) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(dv_base + 2 * (int64_t)row * p.dv_st + 16 * (i % kChunksPerRow)) = make_uint4(0, 0, 0, 0);
-      }
-    }
-    return;
-  }
 
   // a kernel of this library already gave up on a wait: do not pile more work on a sick device
   if (*reinterpret_cast<volatile int*>(&g_status_word) != 0) return;
@@ -274,6 +286,12 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     mbar_init(bar(L::kDkvFull), 1);
     mbar_init(bar(L::kKvFix), 1);
     mbar_init(bar(L::kQdoFix), 1);
+    mbar_init(bar(L::kKvEmpty), 2);  // issuer A (S^T, dP^T) and issuer B (dQ)
+    mbar_init(bar(L::kDkvEmpty), kBwdComputeWarps);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(L::kItemFull + i), 1);
+      mbar_init(bar(L::kItemEmpty + i), kItemReaders);
+    }
     fence_mbar_init();
   }
   if (warp == kBwdProducerWarp && lane == 0) {
@@ -291,8 +309,19 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
+  // Consumer side of the item ring: returns the k-th item of this CTA, or -1 when there is none
+  // (also on a failed wait).  Called by all 32 lanes of a reader warp.
+  auto read_item = [&](int k) -> int {
+    const int slot = k & 1;
+    if (!mbar_wait_warp(bar(L::kItemFull + slot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30)) return -1;
+    const int item = item_ring[slot];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(L::kItemEmpty + slot));
+    return item;
+  };
+
   if (warp == kBwdProducerWarp) {
-    // ============================================================ TMA producer
+    // ============================================================ item scheduler + TMA producer
     // Rows beyond the valid lengths may hold anything (NaN included).  Masked probabilities are
     // exactly zero, but 0 * NaN is NaN inside an MMA, so the padded rows of every tile that is
     // contracted over its rows (K_j for dQ, Q_i for dK, dO_i for dV) are cleared in shared memory.
@@ -305,55 +334,86 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
             make_uint4(0, 0, 0, 0);
       }
     };
-    if (lane == 0) {
-      mbar_expect_tx(bar(L::kKvFull), 2 * kTileBytes);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        tma_load_4d(smem_base + L::kKOff + c * 16384, &k_map, bar(L::kKvFull), c * 64, h, kv0, b);
-        tma_load_4d(smem_base + L::kVOff + c * 16384, &v_map, bar(L::kKvFull), c * 64, h, kv0, b);
-      }
-    }
+    int g = 0;    // query tiles loaded so far (all items)
+    int act = 0;  // items with work so far
     bool ok = true;
-    for (int t = 0; t < n_q && ok; ++t) {
-      const int st = t & 1;
-      const uint32_t ph = (t >> 1) & 1;
-      const int qrow = (i_begin + t) * kBwdTileQ;
-      ok = mbar_wait_warp(bar(L::kQEmpty + st), ph ^ 1, abort_flag, kSiteBase + 1);
+    for (int k = 0; ok; ++k) {
+      const int slot = k & 1;
+      ok = mbar_wait_warp(bar(L::kItemEmpty + slot), ((uint32_t)(k >> 1) & 1u) ^ 1u, abort_flag, kSiteBase + 31);
       if (!ok) break;
+      int item = blockIdx.x;  // the first item needs no ticket
       if (lane == 0) {
-        mbar_expect_tx(bar(L::kQFull + st), kTileBytes);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem_base + L::kQOff + st * kTileBytes + c * 16384, &q_map, bar(L::kQFull + st), c * 64, h, qrow, b);
+        if (k > 0) {
+          const unsigned int tk = atomicAdd(p.ticket, 1u) + gridDim.x;
+          item = tk < (unsigned int)p.n_items ? (int)tk : -1;
+        }
+        item_ring[slot] = item;
+        mbar_arrive(bar(L::kItemFull + slot));
       }
-      ok = mbar_wait_warp(bar(L::kDoEmpty + st), ph ^ 1, abort_flag, kSiteBase + 2);
-      if (!ok) break;
-      if (lane == 0) {
-        mbar_expect_tx(bar(L::kDoFull + st), kTileBytes);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem_base + L::kDoOff + st * kTileBytes + c * 16384, &do_map, bar(L::kDoFull + st), c * 64, h, qrow, b);
-      }
-      if (t == 0 && ragged_kv) {
-        ok = mbar_wait_warp(bar(L::kKvFull), 0, abort_flag, kSiteBase + 17);
+      item = __shfl_sync(0xffffffffu, item, 0);
+      if (item < 0) break;
+      const BwdItem it = bwd_decode_item(p, item);
+      if (it.n_q == 0) continue;
+
+      for (int t = 0; t < it.n_q && ok; ++t) {
+        const int gt = g + t;
+        const int st = gt & 1;
+        const uint32_t ph = (uint32_t)(gt >> 1) & 1u;
+        const int qrow = (it.i_begin + t) * kBwdTileQ;
+        ok = mbar_wait_warp(bar(L::kQEmpty + st), ph ^ 1u, abort_flag, kSiteBase + 1);
         if (!ok) break;
-        zero_rows(smem_gen + L::kKOff, Lk - kv0);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kKvFix));
-      }
-      if (qrow + kBwdTileQ > Lq) {
-        ok = mbar_wait_warp(bar(L::kQFull + st), ph, abort_flag, kSiteBase + 18);
-        ok = ok && mbar_wait_warp(bar(L::kDoFull + st), ph, abort_flag, kSiteBase + 19);
+        if (lane == 0) {
+          mbar_expect_tx(bar(L::kQFull + st), kTileBytes);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(smem_base + L::kQOff + st * kTileBytes + c * 16384, &q_map, bar(L::kQFull + st), c * 64, it.h, qrow, it.b);
+        }
+        ok = mbar_wait_warp(bar(L::kDoEmpty + st), ph ^ 1u, abort_flag, kSiteBase + 2);
         if (!ok) break;
-        zero_rows(smem_gen + L::kQOff + st * kTileBytes, Lq - qrow);
-        zero_rows(smem_gen + L::kDoOff + st * kTileBytes, Lq - qrow);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kQdoFix));
+        if (lane == 0) {
+          mbar_expect_tx(bar(L::kDoFull + st), kTileBytes);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(smem_base + L::kDoOff + st * kTileBytes + c * 16384, &do_map, bar(L::kDoFull + st), c * 64, it.h, qrow, it.b);
+        }
+        if (t == 0) {
+          // K_j, V_j of this item, once the previous item's products have finished reading theirs (the
+          // first Q / dO tiles above are already on their way)
+          if (act > 0) ok = mbar_wait_warp(bar(L::kKvEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 32);
+          if (!ok) break;
+          if (lane == 0) {
+            mbar_expect_tx(bar(L::kKvFull), 2 * kTileBytes);
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+              tma_load_4d(smem_base + L::kKOff + c * 16384, &k_map, bar(L::kKvFull), c * 64, it.h, it.kv0, it.b);
+              tma_load_4d(smem_base + L::kVOff + c * 16384, &v_map, bar(L::kKvFull), c * 64, it.h, it.kv0, it.b);
+            }
+          }
+          if (it.ragged_kv) {
+            ok = mbar_wait_warp(bar(L::kKvFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 17);
+            if (!ok) break;
+            zero_rows(smem_gen + L::kKOff, it.Lk - it.kv0);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(L::kKvFix));
+          }
+        }
+        if (qrow + kBwdTileQ > it.Lq) {
+          ok = mbar_wait_warp(bar(L::kQFull + st), ph, abort_flag, kSiteBase + 18);
+          ok = ok && mbar_wait_warp(bar(L::kDoFull + st), ph, abort_flag, kSiteBase + 19);
+          if (!ok) break;
+          zero_rows(smem_gen + L::kQOff + st * kTileBytes, it.Lq - qrow);
+          zero_rows(smem_gen + L::kDoOff + st * kTileBytes, it.Lq - qrow);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(L::kQdoFix));
+        }
       }
+      g += it.n_q;
+      ++act;
     }
-  } else if (warp == kBwdIssuerA) {
+  }
+  else if (warp == kBwdIssuerA) {
     // ============================================================ issuer A: S^T = K Q^T, dP^T = V dO^T
     const bool leader = elect_one();
     constexpr uint32_t idesc_st = make_idesc(128, 128, kBF16, false, false);
@@ -372,39 +432,59 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         mma_ss(leader, tmem + dcol, make_desc(a_lo + off, hi), make_desc(b_lo + off, hi), idesc_st, kk > 0);
       }
     };
-    bool ok = mbar_wait_warp(bar(L::kKvFull), 0, abort_flag, kSiteBase + 3);
-    if (ragged_kv) ok = ok && mbar_wait_warp(bar(L::kKvFix), 0, abort_flag, kSiteBase + 20);
-    int st = 0;
-    uint32_t ph = 0;  // parity of the stage's "full" barriers
-    for (int t = 0; t < n_q && ok; ++t) {
-      const uint32_t prev = (uint32_t)(t - 1) & 1u;
-      ok = mbar_wait_warp(bar(L::kQFull + st), ph, abort_flag, kSiteBase + 4);
-      if (t == n_q - 1 && ragged_last_q) ok = ok && mbar_wait_warp(bar(L::kQdoFix), 0, abort_flag, kSiteBase + 21);
-      if constexpr (kTwoS) {
-        // this S buffer last held tile t-2: its P^T (read by dV) and then its dQ, until that was drained
-        if (t >= 2) ok = ok && mbar_wait_warp(bar(L::kDqEmpty + sbuf(t)), spar(t - 2), abort_flag, kSiteBase + 5);
-      } else {
-        // the S columns still hold P^T of the previous tile until its dV GEMM has read them
-        if (t > 0) ok = ok && mbar_wait_warp(bar(L::kSFree), prev, abort_flag, kSiteBase + 5);
+    int g = 0;                // query tiles issued so far (all items)
+    uint32_t kv_par = 0u;     // parity of "K_j, V_j loaded": one phase per item with work
+    uint32_t kvfix_par = 0u;  // ... of "padded K rows cleared": one phase per item whose key tile is ragged
+    uint32_t qfix_par = 0u;   // ... of "padded Q / dO rows cleared": one phase per item whose last query tile is ragged
+    bool ok = true;
+    for (int k = 0; ok; ++k) {
+      const int item = read_item(k);
+      if (item < 0) break;
+      const BwdItem it = bwd_decode_item(p, item);
+      if (it.n_q == 0) continue;
+      ok = mbar_wait_warp(bar(L::kKvFull), kv_par, abort_flag, kSiteBase + 3);
+      kv_par ^= 1u;
+      if (it.ragged_kv) {
+        ok = ok && mbar_wait_warp(bar(L::kKvFix), kvfix_par, abort_flag, kSiteBase + 20);
+        kvfix_par ^= 1u;
+      }
+      for (int t = 0; t < it.n_q && ok; ++t) {
+        const int gt = g + t;
+        const int st = gt & 1;
+        const uint32_t ph = (uint32_t)(gt >> 1) & 1u;  // parity of the stage's "full" barriers
+        const uint32_t prev = (uint32_t)(gt - 1) & 1u;
+        ok = mbar_wait_warp(bar(L::kQFull + st), ph, abort_flag, kSiteBase + 4);
+        if (t == it.n_q - 1 && it.ragged_last_q) {
+          ok = ok && mbar_wait_warp(bar(L::kQdoFix), qfix_par, abort_flag, kSiteBase + 21);
+          qfix_par ^= 1u;
+        }
+        if constexpr (kTwoS) {
+          // this S buffer last held tile g-2: its P^T (read by dV) and then its dQ, until that was drained
+          if (gt >= 2) ok = ok && mbar_wait_warp(bar(L::kDqEmpty + sbuf(gt)), spar(gt - 2), abort_flag, kSiteBase + 5);
+        } else {
+          // the S columns still hold P^T of the previous tile until its dV GEMM has read them
+          if (gt > 0) ok = ok && mbar_wait_warp(bar(L::kSFree), prev, abort_flag, kSiteBase + 5);
+        }
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue(kColS + 128u * (uint32_t)sbuf(gt), k_lo, q_lo0 + (uint32_t)st * kStageStep);
+        mma_commit(leader, bar(L::kSFull + sbuf(gt)));
+        mma_commit(leader, bar(L::kQEmpty + st));
+        ok = mbar_wait_warp(bar(L::kDoFull + st), ph, abort_flag, kSiteBase + 6);
+        if (gt > 0) {
+          // the dP columns hold dS^T of the previous tile (read by dK) and, when dQ shares them,
+          // the previous dQ tile until it has been drained
+          ok = ok && mbar_wait_warp(bar(kDqT ? L::kDqEmpty : L::kDpFree), prev, abort_flag, kSiteBase + 7);
+        }
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue(kColDp, v_lo, do_lo0 + (uint32_t)st * kStageStep);
+        mma_commit(leader, bar(L::kDpFull));
+        mma_commit(leader, bar(L::kDoEmpty + st));
       }
       if (!ok) break;
-      tc_fence_after_sync();
-      issue(kColS + 128u * (uint32_t)sbuf(t), k_lo, q_lo0 + (uint32_t)st * kStageStep);
-      mma_commit(leader, bar(L::kSFull + sbuf(t)));
-      mma_commit(leader, bar(L::kQEmpty + st));
-      ok = mbar_wait_warp(bar(L::kDoFull + st), ph, abort_flag, kSiteBase + 6);
-      if (t > 0) {
-        // the dP columns hold dS^T of the previous tile (read by dK) and, when dQ shares them,
-        // the previous dQ tile until it has been drained
-        ok = ok && mbar_wait_warp(bar(kDqT ? L::kDqEmpty : L::kDpFree), prev, abort_flag, kSiteBase + 7);
-      }
-      if (!ok) break;
-      tc_fence_after_sync();
-      issue(kColDp, v_lo, do_lo0 + (uint32_t)st * kStageStep);
-      mma_commit(leader, bar(L::kDpFull));
-      mma_commit(leader, bar(L::kDoEmpty + st));
-      st ^= 1;
-      if (st == 0) ph ^= 1u;
+      mma_commit(leader, bar(L::kKvEmpty));  // this warp's products no longer read K_j, V_j once they complete
+      g += it.n_q;
     }
   } else if (warp == kBwdIssuerB) {
     // ============================================================ issuer B: dV, dK, dQ
@@ -429,195 +509,245 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
                idesc_acc, kk > 0 ? 1u : acc0);
       }
     };
+    int g = 0;    // query tiles issued so far (all items)
+    int act = 0;  // items with work so far
     bool ok = true;
-    int st = 0;
-    for (int t = 0; t < n_q && ok; ++t) {
-      const uint32_t par = (uint32_t)t & 1u;
-      const uint32_t acc0 = t > 0 ? 1u : 0u;
-      // dV += P^T dO
-      ok = mbar_wait_warp(bar(L::kPReady + sbuf(t)), spar(t), abort_flag, kSiteBase + 8);
-      if (!ok) break;
-      tc_fence_after_sync();
-      issue_acc(kColDv, kColS + 128u * (uint32_t)sbuf(t), do_lo0 + (uint32_t)st * kStageStep, acc0);
-      if (!kTwoS) mma_commit(leader, bar(L::kSFree));
-      mma_commit(leader, bar(L::kDoEmpty + st));
-      // dK += dS^T Q
-      ok = mbar_wait_warp(bar(L::kDsReady), par, abort_flag, kSiteBase + 9);
-      if (!ok) break;
-      tc_fence_after_sync();
-      issue_acc(kColDk, kColDp, q_lo0 + (uint32_t)st * kStageStep, acc0);
-      if (!kDqT) mma_commit(leader, bar(L::kDpFree));
-      mma_commit(leader, bar(L::kQEmpty + st));
-      // the dQ GEMM needs the previous dQ tile read out of its columns
-      if constexpr (!kTwoS) {
-        ok = mbar_wait_warp(bar(L::kDqEmpty), par ^ 1u, abort_flag, kSiteBase + 10);
+    for (int k = 0; ok; ++k) {
+      const int item = read_item(k);
+      if (item < 0) break;
+      const BwdItem it = bwd_decode_item(p, item);
+      if (it.n_q == 0) continue;
+      // the accumulators still hold the previous item's dK, dV until the compute warps have read them
+      if (act > 0) ok = mbar_wait_warp(bar(L::kDkvEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 33);
+      for (int t = 0; t < it.n_q && ok; ++t) {
+        const int gt = g + t;
+        const int st = gt & 1;
+        const uint32_t par = (uint32_t)gt & 1u;
+        const uint32_t acc0 = t > 0 ? 1u : 0u;
+        // dV += P^T dO
+        ok = mbar_wait_warp(bar(L::kPReady + sbuf(gt)), spar(gt), abort_flag, kSiteBase + 8);
         if (!ok) break;
         tc_fence_after_sync();
-      }
-      // (two S buffers: dQ goes over this tile's own S^T buffer; dV above, issued by this same
-      //  thread and therefore executed earlier, was the last reader of P^T in it)
+        issue_acc(kColDv, kColS + 128u * (uint32_t)sbuf(gt), do_lo0 + (uint32_t)st * kStageStep, acc0);
+        if (!kTwoS) mma_commit(leader, bar(L::kSFree));
+        mma_commit(leader, bar(L::kDoEmpty + st));
+        // dK += dS^T Q
+        ok = mbar_wait_warp(bar(L::kDsReady), par, abort_flag, kSiteBase + 9);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_acc(kColDk, kColDp, q_lo0 + (uint32_t)st * kStageStep, acc0);
+        if (!kDqT) mma_commit(leader, bar(L::kDpFree));
+        mma_commit(leader, bar(L::kQEmpty + st));
+        // the dQ GEMM needs the previous dQ tile read out of its columns
+        if constexpr (!kTwoS) {
+          ok = mbar_wait_warp(bar(L::kDqEmpty), par ^ 1u, abort_flag, kSiteBase + 10);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+        // (two S buffers: dQ goes over this tile's own S^T buffer; dV above, issued by this same
+        //  thread and therefore executed earlier, was the last reader of P^T in it)
 #pragma unroll
-      for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
-        const uint64_t kd = make_desc(k_lo + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
-        mma_ss(leader, tmem + dq_col(t), kDqT ? kd : dsd, kDqT ? dsd : kd, idesc_dq, kk > 0);
+        for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
+          const uint64_t kd = make_desc(k_lo + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
+          mma_ss(leader, tmem + dq_col(gt), kDqT ? kd : dsd, kDqT ? dsd : kd, idesc_dq, kk > 0);
+        }
+        mma_commit(leader, bar(L::kDqFull + sbuf(gt)));
       }
-      mma_commit(leader, bar(L::kDqFull + sbuf(t)));
-      st ^= 1;
+      if (!ok) break;
+      mma_commit(leader, bar(L::kDkvFull));
+      mma_commit(leader, bar(L::kKvEmpty));  // the dQ products were this warp's readers of K_j
+      g += it.n_q;
+      ++act;
     }
-    if (ok) mma_commit(leader, bar(L::kDkvFull));
-  } else if (warp < kBwdComputeWarps) {
+  }
+  else if (warp < kBwdComputeWarps) {
     // ============================================================ compute warps
     const int quarter = warp & 3;                         // TMEM lane quarter this warp may access
     const int cg = warp >> 2;                             // query-column group: columns 32 cg .. 32 cg + 31
     const int lane_row = quarter * 32 + lane;             // key row within the tile == TMEM lane
-    const int kv = kv0 + lane_row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_addr0 = tmem + lane_addr + kColS + 32 * cg;  // + 128 for the second S buffer
     const uint32_t dp_addr = tmem + lane_addr + kColDp + 32 * cg;
     const float c1 = p.scale * kLog2e;
-    float c0 = p.bias ? p.bias[b] : p.bias_scalar;
-    if (p.score_mod && kv < p.Tk) c0 += p.score_mod[(int64_t)b * p.Tk + kv];
-    c0 *= kLog2e;
-    const bool row_ok = kv < Lk;
     // shared-memory copy of dS^T: [2 blocks of 64 queries][128 key rows][128 bytes], 128-byte swizzle
     const uint32_t ds_line = smem_base + L::kDsOff + (cg >> 1) * 16384 + lane_row * 128;
     const uint32_t chunk0 = (uint32_t)(cg & 1) * 4;
     const uint32_t sw = (uint32_t)(lane_row & 7);
-    bool ok = true;
-
-    // ---- dQ drain (see the file header)
     // D = 128: lane l of quarter k holds d = 32 k + l of dQ^T; this warp takes query columns 32 cg ..
     // D = 64:  this thread holds query row `lane_row`, head columns 16 cg .. 16 cg + 15 of dQ
     const uint32_t dq_off = tmem + lane_addr + (kDqT ? 32 : 16) * cg;
-    auto drain_dq = [&](int t) {  // t = local index of the query tile whose dQ is complete
-      ok = mbar_wait_warp(bar(L::kDqFull + sbuf(t)), spar(t), abort_flag, kSiteBase + 14);
-      const uint32_t dq_addr = dq_off + dq_col(t);
-      if (!ok) return;
-      tc_fence_after_sync();
-      const int q_tile = (i_begin + t) * kBwdTileQ;
-      if constexpr (kDqT) {
-        uint32_t r[32];
-        tmem_ld32_sync(dq_addr, r);
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(t)));  // the TMEM columns are free again
-        const int q_first = q_tile + 32 * cg;
-        float* dst = p.dq_acc + (((int64_t)b * p.Tq + q_first) * p.H + h) * D + lane_row;
-        const int64_t row_stride = (int64_t)p.H * D;
-        const int n_live = min(32, Lq - q_first);  // queries at or beyond Lq get no gradient
-#pragma unroll
-        for (int v = 0; v < 32; ++v) {
-          if (v < n_live)
-            asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + v * row_stride), "f"(__uint_as_float(r[v])) : "memory");
-        }
-      } else {
-        // A warp's reduction instructions are served one 128-byte line at a time (~17 clocks each), so
-        // the number of lines a warp touches is what its stall costs.  This warp therefore takes half
-        // of the head dimension (32 columns = one full line per row) of every second row of its lane
-        // quarter: 16 lines per tile, the minimum for 16 warps.  The rows are regrouped through the
-        // warp's shared-memory patch so that eight adjacent lanes cover the 128 bytes of one row.
-        // (Tried and slower: 64-byte runs of all 32 rows; bulk reductions out of shared memory, which
-        // compete with the tile loads for the copy engine; a separate reduction warp, which serialises.)
-        const int col_half = cg & 1, row_par = cg >> 1;
-        uint32_t r[32];
-        tmem_ld32_sync(dq_off - 16 * cg + dq_col(t) + 32 * col_half, r);
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(t)));
-        uint8_t* patch = smem_gen + L::kDqPatchOff + warp * L::kDqPatchBytes;
-        if ((lane & 1) == row_par) {
-          uint4* mine = reinterpret_cast<uint4*>(patch + (lane >> 1) * L::kDqPatchRow);
-#pragma unroll
-          for (int m = 0; m < 8; ++m) mine[m] = make_uint4(r[4 * m], r[4 * m + 1], r[4 * m + 2], r[4 * m + 3]);
-        }
-        __syncwarp();
-        const int slot = lane >> 3, chunk = lane & 7;  // patch row slot (within a group of four) and 16-byte chunk
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int prow = 4 * k + slot;                                   // patch row = (row within quarter) / 2
-          const int q = q_tile + quarter * 32 + 2 * prow + row_par;
-          const uint4 w = *reinterpret_cast<const uint4*>(patch + prow * L::kDqPatchRow + chunk * 16);
-          if (q < Lq) {  // queries at or beyond Lq get no gradient
-            float* dst = p.dq_acc + (((int64_t)b * p.Tq + q) * p.H + h) * D + 32 * col_half + 4 * chunk;
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(w.x)),
-                         "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
-                         : "memory");
+    int g = 0;    // query tiles processed so far (all items)
+    int act = 0;  // items with work so far
+    bool ok = true;
+
+    for (int k = 0; ok; ++k) {
+      const int item = read_item(k);
+      if (item < 0) break;
+      const BwdItem it = bwd_decode_item(p, item);
+      const int b = it.b, h = it.h, kv0 = it.kv0, Lq = it.Lq, Lk = it.Lk, i_begin = it.i_begin, n_q = it.n_q;
+      const int kv = kv0 + lane_row;
+      uint8_t* dk_base = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((int64_t)b * p.dk_sb + (int64_t)h * p.dk_sh);
+      uint8_t* dv_base = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((int64_t)b * p.dv_sb + (int64_t)h * p.dv_sh);
+      if (n_q == 0) {
+        // no query sees this key tile: its gradients are zero
+        constexpr int kChunksPerRow = D * 2 / 16;
+        for (int i = threadIdx.x; i < kBwdTileKV * kChunksPerRow; i += kBwdComputeWarps * 32) {
+          const int row = kv0 + i / kChunksPerRow;
+          if (row < p.Tk) {
+            *reinterpret_cast<uint4*>(dk_base + 2 * (int64_t)row * p.dk_st + 16 * (i % kChunksPerRow)) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dv_base + 2 * (int64_t)row * p.dv_st + 16 * (i % kChunksPerRow)) = make_uint4(0, 0, 0, 0);
           }
         }
-        __syncwarp();  // the patch is rewritten at the next tile
+        continue;
       }
-    };
+      float c0 = p.bias ? p.bias[b] : p.bias_scalar;
+      if (p.score_mod && kv < p.Tk) c0 += p.score_mod[(int64_t)b * p.Tk + kv];
+      c0 *= kLog2e;
+      const bool row_ok = kv < Lk;
 
-    for (int t = 0; t < n_q; ++t) {
-      const int q0 = (i_begin + t) * kBwdTileQ + 32 * cg;  // first query index of my columns
-      // valid queries for this key row: q_lo <= q < q_hi (empty when the key row is padding)
-      const int q_lo = p.causal ? kv : 0;
-      const int q_hi = row_ok ? Lq : 0;
-      // warp-uniform on purpose: the two instantiations contain warp-collective TMEM accesses
-      const bool need_mask = ragged_kv || (q0 + 32 > Lq) || (p.causal && q0 < kv0 + kBwdTileKV - 1);
-      float pv[32];
-      ok = mbar_wait_warp(bar(L::kSFull + sbuf(t)), spar(t), abort_flag, kSiteBase + 12);
-      const uint32_t s_addr = s_addr0 + 128u * (uint32_t)sbuf(t);
-      if (!ok) break;
-      tc_fence_after_sync();
-      if (need_mask) bwd_phase_a<kBF16, true>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
-      else           bwd_phase_a<kBF16, false>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(L::kPReady + sbuf(t)));
-
-      // dQ of the previous tile is complete by now (or soon): drain it while dP^T is computed.
-      // Its completion also means the dQ GEMM no longer reads the shared-memory copy of dS.
-      if (t > 0) {
-        drain_dq(t - 1);
-        if (!ok) break;
-      }
-
-      ok = mbar_wait_warp(bar(L::kDpFull), (uint32_t)t & 1u, abort_flag, kSiteBase + 13);
-      if (!ok) break;
-      tc_fence_after_sync();
-      if (need_mask) bwd_phase_b<kBF16, true>(dp_addr, ds_line, chunk0, sw, pv);
-      else           bwd_phase_b<kBF16, false>(dp_addr, ds_line, chunk0, sw, pv);
-      fence_proxy_async_smem();
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(L::kDsReady));
-    }
-    if (ok) drain_dq(n_q - 1);
-
-    // ------------------------------------------------------------ epilogue
-    // column groups 0,1 store dV, groups 2,3 store dK (each half of the head dimension)
-    if (ok) ok = mbar_wait_warp(bar(L::kDkvFull), 0, abort_flag, kSiteBase + 15);
-    if (ok) {
-      tc_fence_after_sync();
-      const bool is_dk = cg >= 2;
-      const int col0 = (cg & 1) * (D / 2);
-      const uint32_t acc_addr = tmem + lane_addr + (is_dk ? kColDk : kColDv) + col0;
-      const float mul = is_dk ? p.scale : 1.0f;
-      uint8_t* out_row = (is_dk ? dk_base + 2 * (int64_t)kv * p.dk_st : dv_base + 2 * (int64_t)kv * p.dv_st) + 2 * col0;
+      // ---- dQ drain (see the file header); t = index within the item of the query tile whose dQ is complete
+      auto drain_dq = [&](int t) {
+        const int gt = g + t;
+        ok = mbar_wait_warp(bar(L::kDqFull + sbuf(gt)), spar(gt), abort_flag, kSiteBase + 14);
+        const uint32_t dq_addr = dq_off + dq_col(gt);
+        if (!ok) return;
+        tc_fence_after_sync();
+        const int q_tile = (i_begin + t) * kBwdTileQ;
+        if constexpr (kDqT) {
+          uint32_t r[32];
+          tmem_ld32_sync(dq_addr, r);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(gt)));  // the TMEM columns are free again
+          const int q_first = q_tile + 32 * cg;
+          float* dst = p.dq_acc + (((int64_t)b * p.Tq + q_first) * p.H + h) * D + lane_row;
+          const int64_t row_stride = (int64_t)p.H * D;
+          const int n_live = min(32, Lq - q_first);  // queries at or beyond Lq get no gradient
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        uint32_t r[32];
-        tmem_ld32_sync(acc_addr + c * 32, r);
-        if (kv < p.Tk) {
+          for (int v = 0; v < 32; ++v) {
+            if (v < n_live)
+              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + v * row_stride), "f"(__uint_as_float(r[v])) : "memory");
+          }
+        } else {
+          // A warp's reduction instructions are served one 128-byte line at a time (~17 clocks each), so
+          // the number of lines a warp touches is what its stall costs.  This warp therefore takes half
+          // of the head dimension (32 columns = one full line per row) of every second row of its lane
+          // quarter: 16 lines per tile, the minimum for 16 warps.  The rows are regrouped through the
+          // warp's shared-memory patch so that eight adjacent lanes cover the 128 bytes of one row.
+          // (Tried and slower: 64-byte runs of all 32 rows; bulk reductions out of shared memory, which
+          // compete with the tile loads for the copy engine; a separate reduction warp, which serialises.)
+          const int col_half = cg & 1, row_par = cg >> 1;
+          uint32_t r[32];
+          tmem_ld32_sync(dq_off - 16 * cg + dq_col(gt) + 32 * col_half, r);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(gt)));
+          uint8_t* patch = smem_gen + L::kDqPatchOff + warp * L::kDqPatchBytes;
+          if ((lane & 1) == row_par) {
+            uint4* mine = reinterpret_cast<uint4*>(patch + (lane >> 1) * L::kDqPatchRow);
+#pragma unroll
+            for (int m = 0; m < 8; ++m) mine[m] = make_uint4(r[4 * m], r[4 * m + 1], r[4 * m + 2], r[4 * m + 3]);
+          }
+          __syncwarp();
+          const int slot = lane >> 3, chunk = lane & 7;  // patch row slot (within a group of four) and 16-byte chunk
+#pragma unroll
+          for (int kq = 0; kq < 4; ++kq) {
+            const int prow = 4 * kq + slot;                                  // patch row = (row within quarter) / 2
+            const int q = q_tile + quarter * 32 + 2 * prow + row_par;
+            const uint4 w = *reinterpret_cast<const uint4*>(patch + prow * L::kDqPatchRow + chunk * 16);
+            if (q < Lq) {  // queries at or beyond Lq get no gradient
+              float* dst = p.dq_acc + (((int64_t)b * p.Tq + q) * p.H + h) * D + 32 * col_half + 4 * chunk;
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(w.x)),
+                           "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
+                           : "memory");
+            }
+          }
+          __syncwarp();  // the patch is rewritten at the next tile
+        }
+      };
+
+      for (int t = 0; t < n_q; ++t) {
+        const int gt = g + t;
+        const int q0 = (i_begin + t) * kBwdTileQ + 32 * cg;  // first query index of my columns
+        // valid queries for this key row: q_lo <= q < q_hi (empty when the key row is padding)
+        const int q_lo = p.causal ? kv : 0;
+        const int q_hi = row_ok ? Lq : 0;
+        // warp-uniform on purpose: the two instantiations contain warp-collective TMEM accesses
+        const bool need_mask = it.ragged_kv || (q0 + 32 > Lq) || (p.causal && q0 < kv0 + kBwdTileKV - 1);
+        float pv[32];
+        ok = mbar_wait_warp(bar(L::kSFull + sbuf(gt)), spar(gt), abort_flag, kSiteBase + 12);
+        const uint32_t s_addr = s_addr0 + 128u * (uint32_t)sbuf(gt);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (need_mask) bwd_phase_a<kBF16, true>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
+        else           bwd_phase_a<kBF16, false>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kPReady + sbuf(gt)));
+
+        // dQ of the previous tile is complete by now (or soon): drain it while dP^T is computed.
+        // Its completion also means the dQ GEMM no longer reads the shared-memory copy of dS.
+        if (t > 0) {
+          drain_dq(t - 1);
+          if (!ok) break;
+        }
+
+        ok = mbar_wait_warp(bar(L::kDpFull), (uint32_t)gt & 1u, abort_flag, kSiteBase + 13);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (need_mask) bwd_phase_b<kBF16, true>(dp_addr, ds_line, chunk0, sw, pv);
+        else           bwd_phase_b<kBF16, false>(dp_addr, ds_line, chunk0, sw, pv);
+        fence_proxy_async_smem();
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kDsReady));
+      }
+      if (ok) drain_dq(n_q - 1);
+
+      // ------------------------------------------------------------ epilogue of the item
+      // column groups 0,1 store dV, groups 2,3 store dK (each half of the head dimension)
+      if (ok) ok = mbar_wait_warp(bar(L::kDkvFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 15);
+      if (!ok) break;
+      {
+        tc_fence_after_sync();
+        const bool is_dk = cg >= 2;
+        const int col0 = (cg & 1) * (D / 2);
+        const uint32_t acc_addr = tmem + lane_addr + (is_dk ? kColDk : kColDv) + col0;
+        const float mul = is_dk ? p.scale : 1.0f;
+        // out of TMEM already rounded to 16 bits, so that few registers are live across the hand-over
+        uint4 w[D / 64][4];
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t r[32];
+          tmem_ld32_sync(acc_addr + c * 32, r);
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 w;
-            w.x = pack2<kBF16>(mul * __uint_as_float(r[8 * q4 + 0]), mul * __uint_as_float(r[8 * q4 + 1]));
-            w.y = pack2<kBF16>(mul * __uint_as_float(r[8 * q4 + 2]), mul * __uint_as_float(r[8 * q4 + 3]));
-            w.z = pack2<kBF16>(mul * __uint_as_float(r[8 * q4 + 4]), mul * __uint_as_float(r[8 * q4 + 5]));
-            w.w = pack2<kBF16>(mul * __uint_as_float(r[8 * q4 + 6]), mul * __uint_as_float(r[8 * q4 + 7]));
-            if (!row_ok) w = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(out_row + 64 * c + 16 * q4) = w;
+            w[c][q4].x = pack2<kBF16>(mul * __uint_as_float(r[8 * q4 + 0]), mul * __uint_as_float(r[8 * q4 + 1]));
+            w[c][q4].y = pack2<kBF16>(mul * __uint_as_float(r[8 * q4 + 2]), mul * __uint_as_float(r[8 * q4 + 3]));
+            w[c][q4].z = pack2<kBF16>(mul * __uint_as_float(r[8 * q4 + 4]), mul * __uint_as_float(r[8 * q4 + 5]));
+            w[c][q4].w = pack2<kBF16>(mul * __uint_as_float(r[8 * q4 + 6]), mul * __uint_as_float(r[8 * q4 + 7]));
+            if (!row_ok) w[c][q4] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        // the accumulators are in registers: the next item's first dV / dK products may overwrite them
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
+        if (kv < p.Tk) {
+          uint8_t* out_row = (is_dk ? dk_base + 2 * (int64_t)kv * p.dk_st : dv_base + 2 * (int64_t)kv * p.dv_st) + 2 * col0;
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(out_row + 64 * c + 16 * q4) = w[c][q4];
           }
         }
       }
+      g += n_q;
+      ++act;
     }
   }
-
-
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before_sync();
@@ -625,6 +755,16 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   if (warp == kBwdIssuerA) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
+  }
+  if (threadIdx.x == 0) {
+    // the last CTA to finish leaves both counters at zero for the next launch that uses them
+    __threadfence();
+    const unsigned int done = atomicAdd(p.ticket + 1, 1u);
+    if (done == gridDim.x - 1) {
+      p.ticket[0] = 0u;
+      p.ticket[1] = 0u;
+      __threadfence();
+    }
   }
 }
 

@@ -126,12 +126,12 @@ int set_smem(K kernel, int bytes) {
   return 0;
 }
 
-// Work-item counters of the persistent forward kernel: a ring of (next item, finished CTAs) pairs.
+// Work-item counters of the persistent kernels (forward and backward): a ring of (next item, finished CTAs) pairs.
 // Each launch takes the next pair; the kernel leaves its pair at zero when its last CTA finishes,
-// so a pair is only in doubt if more than kTicketSlots forward launches are in flight at once on
+// so a pair is only in doubt if more than kTicketSlots launches are in flight at once on
 // one device.
 constexpr int kTicketSlots = 1024;
-__device__ unsigned int g_fwd_tickets[2 * kTicketSlots];
+__device__ unsigned int g_item_tickets[2 * kTicketSlots];
 
 struct FwdDeviceInfo {
   unsigned int* tickets = nullptr;
@@ -147,9 +147,9 @@ int fwd_device_info(int device, FwdDeviceInfo* out) {
   std::lock_guard<std::mutex> lock(mu);
   if (!cached[device].tickets) {
     unsigned int* ptr = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_fwd_tickets);
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_item_tickets);
     if (e != cudaSuccess || !ptr)
-      return fail(-100, "cudaGetSymbolAddress(forward item counters) failed on device %d: %s", device,
+      return fail(-100, "cudaGetSymbolAddress(work-item counters) failed on device %d: %s", device,
                   cudaGetErrorString(e));
     int n_sm = 0;
     SIG_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
@@ -159,6 +159,12 @@ int fwd_device_info(int device, FwdDeviceInfo* out) {
   }
   *out = cached[device];
   return 0;
+}
+
+// The pair of counters for one launch.
+unsigned int* next_ticket_pair(const FwdDeviceInfo& info, int device) {
+  static std::atomic<unsigned int> next_slot[64];
+  return info.tickets + 2 * (next_slot[device].fetch_add(1u) % kTicketSlots);
 }
 
 template <int D, bool kBF16, bool kScoreMod>
@@ -189,8 +195,7 @@ int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   fp.n_items = (int)n_items;
   FwdDeviceInfo info;
   if (int rc = fwd_device_info(p->device, &info)) return rc;
-  static std::atomic<unsigned int> next_slot[64];
-  fp.ticket = info.tickets + 2 * (next_slot[p->device].fetch_add(1u) % kTicketSlots);
+  fp.ticket = next_ticket_pair(info, p->device);
   // persistent: one CTA per SM (the kernel's shared memory allows no more), fewer when there are fewer items
   dim3 grid((unsigned int)std::min<int64_t>(n_items, info.n_sm));
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
@@ -228,12 +233,19 @@ int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   bp.B = p->B; bp.H = p->H; bp.Tq = p->Tq; bp.Tk = p->Tk;
   bp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
   bp.n_kvblk = (p->Tk + kBwdTileKV - 1) / kBwdTileKV;
+  const int64_t n_items = (int64_t)bp.n_kvblk * p->H * p->B;
+  if (n_items > INT32_MAX) return fail(-2, "too many (batch, head, key tile) items: %lld", (long long)n_items);
+  bp.n_items = (int)n_items;
+  FwdDeviceInfo info;
+  if (int rc = fwd_device_info(p->device, &info)) return rc;
+  bp.ticket = next_ticket_pair(info, p->device);
 
   {
     auto kernel = sigattn_bwd_kernel<D, kBF16>;
     constexpr int smem = BwdSmem<D>::kDynBytes;
     if (int rc = set_smem(kernel, smem)) return rc;
-    dim3 grid(bp.n_kvblk, p->H, p->B);
+    // persistent: one CTA per SM (the kernel's shared memory allows no more), fewer when there are fewer items
+    dim3 grid((unsigned int)std::min<int64_t>(n_items, info.n_sm));
     if (p->ev_main_start) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream));
     kernel<<<grid, kBwdThreads, smem, stream>>>(qm, km, vm, dom, bp);
     SIG_CUDA(cudaGetLastError());
