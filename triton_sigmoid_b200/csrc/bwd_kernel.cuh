@@ -81,9 +81,12 @@ template <int D>
 struct BwdSmem {
   static constexpr int kStages = 2;
   static constexpr int kTileBytes = 128 * D * 2;
+  // K_j / V_j buffers: two at D = 64 (the next item's are loaded while this item still computes), one at
+  // D = 128 (no room for more)
+  static constexpr int kKvBufs = (D == 64) ? 2 : 1;
   static constexpr int kKOff = 0;
-  static constexpr int kVOff = kKOff + kTileBytes;
-  static constexpr int kQOff = kVOff + kTileBytes;
+  static constexpr int kVOff = kKOff + kKvBufs * kTileBytes;
+  static constexpr int kQOff = kVOff + kKvBufs * kTileBytes;
   static constexpr int kDoOff = kQOff + kStages * kTileBytes;
   static constexpr int kDsOff = kDoOff + kStages * kTileBytes;
   static constexpr int kDsBytes = 128 * 128 * 2;
@@ -94,8 +97,8 @@ struct BwdSmem {
   static constexpr int kDqPatchOff = kDsOff + kDsBytes;
   static constexpr int kDqPatchBytes = (D == 64) ? 16 * kDqPatchRow : 0;
   static constexpr int kBarOff = kDqPatchOff + 16 * kDqPatchBytes;
-  static constexpr int kKvFull = 0;
-  static constexpr int kQFull = 1;                    // [2]
+  static constexpr int kKvFull = 0;                   // [2] per K/V buffer
+  static constexpr int kQFull = 2;                    // [2]
   static constexpr int kQEmpty = kQFull + kStages;    // [2]  both issuers release a stage
   static constexpr int kDoFull = kQEmpty + kStages;   // [2]
   static constexpr int kDoEmpty = kDoFull + kStages;  // [2]
@@ -108,10 +111,10 @@ struct BwdSmem {
   static constexpr int kDqFull = kDpFree + 1;         // [2] dQ tile complete in TMEM
   static constexpr int kDqEmpty = kDqFull + 2;        // [2] dQ tile read out (16 warps)
   static constexpr int kDkvFull = kDqEmpty + 2;       // every MMA of the CTA complete
-  static constexpr int kKvFix = kDkvFull + 1;         // padded rows of K_j zeroed
-  static constexpr int kQdoFix = kKvFix + 1;          // padded rows of the last Q_i / dO_i zeroed
-  static constexpr int kKvEmpty = kQdoFix + 1;        // both issuers: every product that reads K_j / V_j is complete
-  static constexpr int kDkvEmpty = kKvEmpty + 1;      // dK_j, dV_j read out of TMEM (16 warps)
+  static constexpr int kKvFix = kDkvFull + 1;         // [2] per K/V buffer: padded rows of K_j zeroed
+  static constexpr int kQdoFix = kKvFix + 2;          // [2] per stage: padded rows of the last Q_i / dO_i zeroed
+  static constexpr int kKvEmpty = kQdoFix + 2;        // [2] per K/V buffer, both issuers: every product that reads it is complete
+  static constexpr int kDkvEmpty = kKvEmpty + 2;      // dK_j, dV_j read out of TMEM (16 warps)
   static constexpr int kItemFull = kDkvEmpty + 1;     // [2] item index published
   static constexpr int kItemEmpty = kItemFull + 2;    // [2] item index read by every consumer warp
   static constexpr int kNumBars = kItemEmpty + 2;
@@ -264,7 +267,12 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   // ---------------------------------------------------------------- setup
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(bar(L::kKvFull), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(L::kKvFull + i), 1);
+      mbar_init(bar(L::kKvFix + i), 1);
+      mbar_init(bar(L::kQdoFix + i), 1);
+      mbar_init(bar(L::kKvEmpty + i), 2);  // issuer A (S^T, dP^T) and issuer B (dQ)
+    }
     for (int i = 0; i < L::kStages; ++i) {
       mbar_init(bar(L::kQFull + i), 1);
       mbar_init(bar(L::kQEmpty + i), 2);   // S^T (issuer A) and dK (issuer B) both read Q_i
@@ -284,9 +292,6 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     mbar_init(bar(L::kDqEmpty + 0), kBwdComputeWarps);
     mbar_init(bar(L::kDqEmpty + 1), kBwdComputeWarps);
     mbar_init(bar(L::kDkvFull), 1);
-    mbar_init(bar(L::kKvFix), 1);
-    mbar_init(bar(L::kQdoFix), 1);
-    mbar_init(bar(L::kKvEmpty), 2);  // issuer A (S^T, dP^T) and issuer B (dQ)
     mbar_init(bar(L::kDkvEmpty), kBwdComputeWarps);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(L::kItemFull + i), 1);
@@ -377,25 +382,27 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
             tma_load_4d(smem_base + L::kDoOff + st * kTileBytes + c * 16384, &do_map, bar(L::kDoFull + st), c * 64, it.h, qrow, it.b);
         }
         if (t == 0) {
-          // K_j, V_j of this item, once the previous item's products have finished reading theirs (the
-          // first Q / dO tiles above are already on their way)
-          if (act > 0) ok = mbar_wait_warp(bar(L::kKvEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 32);
+          // K_j, V_j of this item into buffer kb, once the products of the item that used it last have
+          // finished reading it (the first Q / dO tiles above are already on their way)
+          const int kb = act % L::kKvBufs;
+          const uint32_t kph = (uint32_t)(act / L::kKvBufs) & 1u;
+          ok = mbar_wait_warp(bar(L::kKvEmpty + kb), kph ^ 1u, abort_flag, kSiteBase + 32);
           if (!ok) break;
           if (lane == 0) {
-            mbar_expect_tx(bar(L::kKvFull), 2 * kTileBytes);
+            mbar_expect_tx(bar(L::kKvFull + kb), 2 * kTileBytes);
 #pragma unroll
             for (int c = 0; c < D / 64; ++c) {
-              tma_load_4d(smem_base + L::kKOff + c * 16384, &k_map, bar(L::kKvFull), c * 64, it.h, it.kv0, it.b);
-              tma_load_4d(smem_base + L::kVOff + c * 16384, &v_map, bar(L::kKvFull), c * 64, it.h, it.kv0, it.b);
+              tma_load_4d(smem_base + L::kKOff + kb * kTileBytes + c * 16384, &k_map, bar(L::kKvFull + kb), c * 64, it.h, it.kv0, it.b);
+              tma_load_4d(smem_base + L::kVOff + kb * kTileBytes + c * 16384, &v_map, bar(L::kKvFull + kb), c * 64, it.h, it.kv0, it.b);
             }
           }
           if (it.ragged_kv) {
-            ok = mbar_wait_warp(bar(L::kKvFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 17);
+            ok = mbar_wait_warp(bar(L::kKvFull + kb), kph, abort_flag, kSiteBase + 17);
             if (!ok) break;
-            zero_rows(smem_gen + L::kKOff, it.Lk - it.kv0);
+            zero_rows(smem_gen + L::kKOff + kb * kTileBytes, it.Lk - it.kv0);
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(L::kKvFix));
+            if (lane == 0) mbar_arrive(bar(L::kKvFix + kb));
           }
         }
         if (qrow + kBwdTileQ > it.Lq) {
@@ -406,7 +413,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           zero_rows(smem_gen + L::kDoOff + st * kTileBytes, it.Lq - qrow);
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(L::kQdoFix));
+          if (lane == 0) mbar_arrive(bar(L::kQdoFix + st));
         }
       }
       g += it.n_q;
@@ -433,20 +440,21 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       }
     };
     int g = 0;                // query tiles issued so far (all items)
-    uint32_t kv_par = 0u;     // parity of "K_j, V_j loaded": one phase per item with work
-    uint32_t kvfix_par = 0u;  // ... of "padded K rows cleared": one phase per item whose key tile is ragged
-    uint32_t qfix_par = 0u;   // ... of "padded Q / dO rows cleared": one phase per item whose last query tile is ragged
+    int act = 0;              // items with work so far
+    uint32_t kvfix_par = 0u;  // bit kb: parity of buffer kb's "padded K rows cleared" (one phase per ragged key tile in it)
+    uint32_t qfix_par = 0u;   // bit st: parity of stage st's "padded Q / dO rows cleared"
     bool ok = true;
     for (int k = 0; ok; ++k) {
       const int item = read_item(k);
       if (item < 0) break;
       const BwdItem it = bwd_decode_item(p, item);
       if (it.n_q == 0) continue;
-      ok = mbar_wait_warp(bar(L::kKvFull), kv_par, abort_flag, kSiteBase + 3);
-      kv_par ^= 1u;
+      const int kb = act % L::kKvBufs;
+      const uint32_t kv_off = (uint32_t)kb * kStageStep;  // this item's K_j / V_j buffer, in descriptor address units
+      ok = mbar_wait_warp(bar(L::kKvFull + kb), (uint32_t)(act / L::kKvBufs) & 1u, abort_flag, kSiteBase + 3);
       if (it.ragged_kv) {
-        ok = ok && mbar_wait_warp(bar(L::kKvFix), kvfix_par, abort_flag, kSiteBase + 20);
-        kvfix_par ^= 1u;
+        ok = ok && mbar_wait_warp(bar(L::kKvFix + kb), (kvfix_par >> kb) & 1u, abort_flag, kSiteBase + 20);
+        kvfix_par ^= 1u << kb;
       }
       for (int t = 0; t < it.n_q && ok; ++t) {
         const int gt = g + t;
@@ -455,8 +463,8 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         const uint32_t prev = (uint32_t)(gt - 1) & 1u;
         ok = mbar_wait_warp(bar(L::kQFull + st), ph, abort_flag, kSiteBase + 4);
         if (t == it.n_q - 1 && it.ragged_last_q) {
-          ok = ok && mbar_wait_warp(bar(L::kQdoFix), qfix_par, abort_flag, kSiteBase + 21);
-          qfix_par ^= 1u;
+          ok = ok && mbar_wait_warp(bar(L::kQdoFix + st), (qfix_par >> st) & 1u, abort_flag, kSiteBase + 21);
+          qfix_par ^= 1u << st;
         }
         if constexpr (kTwoS) {
           // this S buffer last held tile g-2: its P^T (read by dV) and then its dQ, until that was drained
@@ -467,7 +475,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         }
         if (!ok) break;
         tc_fence_after_sync();
-        issue(kColS + 128u * (uint32_t)sbuf(gt), k_lo, q_lo0 + (uint32_t)st * kStageStep);
+        issue(kColS + 128u * (uint32_t)sbuf(gt), k_lo + kv_off, q_lo0 + (uint32_t)st * kStageStep);
         mma_commit(leader, bar(L::kSFull + sbuf(gt)));
         mma_commit(leader, bar(L::kQEmpty + st));
         ok = mbar_wait_warp(bar(L::kDoFull + st), ph, abort_flag, kSiteBase + 6);
@@ -478,13 +486,14 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         }
         if (!ok) break;
         tc_fence_after_sync();
-        issue(kColDp, v_lo, do_lo0 + (uint32_t)st * kStageStep);
+        issue(kColDp, v_lo + kv_off, do_lo0 + (uint32_t)st * kStageStep);
         mma_commit(leader, bar(L::kDpFull));
         mma_commit(leader, bar(L::kDoEmpty + st));
       }
       if (!ok) break;
-      mma_commit(leader, bar(L::kKvEmpty));  // this warp's products no longer read K_j, V_j once they complete
+      mma_commit(leader, bar(L::kKvEmpty + kb));  // this warp's products no longer read K_j, V_j once they complete
       g += it.n_q;
+      ++act;
     }
   } else if (warp == kBwdIssuerB) {
     // ============================================================ issuer B: dV, dK, dQ
@@ -517,6 +526,8 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       if (item < 0) break;
       const BwdItem it = bwd_decode_item(p, item);
       if (it.n_q == 0) continue;
+      const int kb = act % L::kKvBufs;
+      const uint32_t kv_off = (uint32_t)kb * kStageStep;
       // the accumulators still hold the previous item's dK, dV until the compute warps have read them
       if (act > 0) ok = mbar_wait_warp(bar(L::kDkvEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 33);
       for (int t = 0; t < it.n_q && ok; ++t) {
@@ -538,6 +549,8 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         issue_acc(kColDk, kColDp, q_lo0 + (uint32_t)st * kStageStep, acc0);
         if (!kDqT) mma_commit(leader, bar(L::kDpFree));
         mma_commit(leader, bar(L::kQEmpty + st));
+        // dK_j, dV_j are complete with the last tile's dK: the epilogue need not wait for its dQ
+        if (t == it.n_q - 1) mma_commit(leader, bar(L::kDkvFull));
         // the dQ GEMM needs the previous dQ tile read out of its columns
         if constexpr (!kTwoS) {
           ok = mbar_wait_warp(bar(L::kDqEmpty), par ^ 1u, abort_flag, kSiteBase + 10);
@@ -548,14 +561,13 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         //  thread and therefore executed earlier, was the last reader of P^T in it)
 #pragma unroll
         for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
-          const uint64_t kd = make_desc(k_lo + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
+          const uint64_t kd = make_desc(k_lo + kv_off + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
           mma_ss(leader, tmem + dq_col(gt), kDqT ? kd : dsd, kDqT ? dsd : kd, idesc_dq, kk > 0);
         }
         mma_commit(leader, bar(L::kDqFull + sbuf(gt)));
       }
       if (!ok) break;
-      mma_commit(leader, bar(L::kDkvFull));
-      mma_commit(leader, bar(L::kKvEmpty));  // the dQ products were this warp's readers of K_j
+      mma_commit(leader, bar(L::kKvEmpty + kb));  // the dQ products were this warp's readers of K_j
       g += it.n_q;
       ++act;
     }
@@ -704,11 +716,12 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kDsReady));
       }
-      if (ok) drain_dq(n_q - 1);
+      if (!ok) break;
 
       // ------------------------------------------------------------ epilogue of the item
+      // (before the drain of the last dQ tile, whose product is still running)
       // column groups 0,1 store dV, groups 2,3 store dK (each half of the head dimension)
-      if (ok) ok = mbar_wait_warp(bar(L::kDkvFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 15);
+      ok = mbar_wait_warp(bar(L::kDkvFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 15);
       if (!ok) break;
       {
         tc_fence_after_sync();
@@ -744,6 +757,8 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           }
         }
       }
+      drain_dq(n_q - 1);
+      if (!ok) break;
       g += n_q;
       ++act;
     }
