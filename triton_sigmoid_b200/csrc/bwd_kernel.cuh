@@ -133,20 +133,37 @@ __device__ __forceinline__ void bwd_phase_a(uint32_t s_addr, float c1, float c0,
   tmem_ld32_sync(s_addr, r);
   uint32_t pk[16];
   float2 t[16];
+  // unmasked tiles work on logits shifted up by kDeepShift (see sigmoid2_from_shifted_log2_deep)
+  const float c0s = kMask ? c0 : c0 + kDeepShift;
 #pragma unroll
   for (int i = 0; i < 16; ++i)
     t[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), make_float2(c1, c1),
-                      make_float2(c0, c0));
-  // all logits negative (the usual case under the default bias): no compare / select per element
+                      make_float2(c0s, c0s));
+  // all logits far below zero (the usual case under the default bias): short series, no compare / select per element
   if (!kMask && warp_all_negative(t)) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float2 pe = sigmoid2_from_log2_neg<kBF16>(t[i]);
+      const float2 pe = sigmoid2_from_shifted_log2_deep<kBF16>(t[i]);
       pv[2 * i] = pe.x;
       pv[2 * i + 1] = pe.y;
       pk[i] = pack2<kBF16>(pe.x, pe.y);
     }
   } else {
+    bool all_neg = false;
+    if constexpr (!kMask) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) t[i] = __fadd2_rn(t[i], make_float2(-kDeepShift, -kDeepShift));
+      all_neg = warp_all_negative(t);  // negative but not far below zero: full polynomial, still no select
+    }
+    if (all_neg) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float2 pe = sigmoid2_from_log2_neg<kBF16>(t[i]);
+        pv[2 * i] = pe.x;
+        pv[2 * i + 1] = pe.y;
+        pk[i] = pack2<kBF16>(pe.x, pe.y);
+      }
+    } else
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       float2 pe = sigmoid2_from_log2<kBF16>(t[i]);

@@ -148,10 +148,12 @@ __device__ __forceinline__ void fwd_sigmoid_half_tile(uint32_t s_addr, float c1,
     if (c + 1 < kNCh) tmem_ld(s_addr + (c + 1) * kCh, rbuf[(c + 1) & 1]);
     uint32_t pk[kCh / 2];
     float2 t[kCh / 2];
+    // unmasked tiles work on logits shifted up by kDeepShift (see sigmoid2_from_shifted_log2_deep)
+    const float c0s = kMask ? c0 : c0 + kDeepShift;
 #pragma unroll
     for (int i = 0; i < kCh / 2; ++i) {
       t[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), make_float2(c1, c1),
-                        make_float2(c0, c0));
+                        make_float2(c0s, c0s));
     }
     if constexpr (kScoreMod) {
       // per-key additive bias: the same value for every lane (row), read through the read-only path
@@ -172,15 +174,28 @@ __device__ __forceinline__ void fwd_sigmoid_half_tile(uint32_t s_addr, float c1,
         }
       }
     }
-    // Under the default bias every logit of a chunk is negative: then the sign handling (one
-    // compare and one select per element) is skipped for the whole warp.
+    // Under the default bias every logit of a chunk is far below zero: the short series applies
+    // and the sign handling (one compare and one select per element) is skipped for the whole warp.
     if (!kMask && warp_all_negative(t)) {
 #pragma unroll
       for (int i = 0; i < kCh / 2; ++i) {
-        const float2 pr = sigmoid2_from_log2_neg<kBF16>(t[i]);
+        const float2 pr = sigmoid2_from_shifted_log2_deep<kBF16>(t[i]);
         pk[i] = pack2<kBF16>(pr.x, pr.y);
       }
     } else {
+      bool all_neg = false;
+      if constexpr (!kMask) {
+#pragma unroll
+        for (int i = 0; i < kCh / 2; ++i) t[i] = __fadd2_rn(t[i], make_float2(-kDeepShift, -kDeepShift));
+        all_neg = warp_all_negative(t);  // negative but not far below zero: full polynomial, still no select
+      }
+      if (all_neg) {
+#pragma unroll
+        for (int i = 0; i < kCh / 2; ++i) {
+          const float2 pr = sigmoid2_from_log2_neg<kBF16>(t[i]);
+          pk[i] = pack2<kBF16>(pr.x, pr.y);
+        }
+      } else
 #pragma unroll
       for (int i = 0; i < kCh / 2; ++i) {
         float2 pr = sigmoid2_from_log2<kBF16>(t[i]);

@@ -51,6 +51,29 @@ __device__ __forceinline__ float2 sigmoid2_from_log2_neg(float2 t) {
   return __fmul2_rn(e, rcp1p_poly<kBF16>(e));
 }
 
+// Far below zero the series sigmoid(x) = e - e^2 + e^3 - ... (e = exp(x)) needs very few terms.  The
+// kernels evaluate their logits shifted up by kDeepShift (in the base-2 domain, folded into the bias
+// they add anyway), u = t + kDeepShift, so that "every logit of the warp is below -kDeepShift" is the
+// same sign-bit test as warp_all_negative(); that is the usual case under the default bias -log(T)
+// (a typical probability is 1/T).  With e' = 2^u = 2^kDeepShift e:
+//   fp16: p = e' (a + e' (b + e' c)),  a = 2^-5, b = -2^-10, c = 2^-15   (relative error < e^3 <= 3.1e-5)
+//   bf16: p = e' (a + e' b)                                             (relative error < e^2 <= 9.8e-4)
+// i.e. two or three packed operations after the exponential instead of four or five.
+constexpr float kDeepShift = 5.0f;
+template <bool kBF16>
+__device__ __forceinline__ float2 sigmoid2_from_shifted_log2_deep(float2 u) {
+  const float2 e = make_float2(ex2_approx(u.x), ex2_approx(u.y));
+  constexpr float a = 0.03125f, b = -0.0009765625f, c = 0.000030517578125f;
+  float2 r;
+  if constexpr (kBF16) {
+    r = __ffma2_rn(e, make_float2(b, b), make_float2(a, a));
+  } else {
+    r = __ffma2_rn(e, make_float2(c, c), make_float2(b, b));
+    r = __ffma2_rn(r, e, make_float2(a, a));
+  }
+  return __fmul2_rn(e, r);
+}
+
 // True when every one of a warp's logits t[0..N) (all 32 lanes) is negative: AND of the sign bits.
 template <int N>
 __device__ __forceinline__ bool warp_all_negative(const float2 (&t)[N]) {
