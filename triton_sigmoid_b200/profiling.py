@@ -61,3 +61,27 @@ def time_main_kernel(direction: str, q, k, v, dout=None, seq_lens_q=None, seq_le
         pairs.append((e0, e1))
     torch.cuda.synchronize(q.device)
     return [a.elapsed_time(b) for a, b in pairs]
+
+
+def _main() -> None:
+    """``python -m triton_sigmoid_b200.profiling B N H D fp16|bf16|fp32 [causal]``: one forward and one
+    backward of that shape through the public API (seed 0), for a profiler to capture."""
+    import sys
+
+    from .ops import sigmoid_attention
+
+    B, N, H, D = (int(x) for x in sys.argv[1:5])
+    dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}[sys.argv[5] if len(sys.argv) > 5 else "fp16"]
+    causal = len(sys.argv) > 6 and sys.argv[6] == "causal"
+    torch.manual_seed(0)
+    q, k, v, do = (torch.randn(B, N, H, D, device="cuda", dtype=dtype) for _ in range(4))
+    for t in (q, k, v):
+        t.requires_grad_()
+    out = sigmoid_attention(q, k, v, is_causal=causal)
+    out.backward(do)
+    torch.cuda.synchronize()
+    print("ok", float(out.detach().float().abs().mean()), float(q.grad.float().abs().mean()))
+
+
+if __name__ == "__main__":
+    _main()
