@@ -119,3 +119,29 @@ def test_forward_is_deterministic():
     l = _lens(3, 640, 0.3, 3)
     a = m.sigmoid_attention_padded(q, k, v, seq_lens_k=l, seq_lens_q=l, is_causal=True)
     assert torch.equal(a, m.sigmoid_attention_padded(q, k, v, seq_lens_k=l, seq_lens_q=l, is_causal=True))
+
+
+@pytest.mark.parametrize("D,dtype", [(64, torch.float16), (128, torch.bfloat16)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_many_items_with_mixed_lengths_against_gpu_fp32_math(D, dtype, causal):
+    """Several times more (batch, head, block) items than SMs, with empty, ragged and full ones mixed:
+    every CTA of the persistent kernels walks through all kinds of items, in an order that depends
+    on timing.  Compared with fp32 torch math on the GPU; padded rows must be exactly zero."""
+    B, T, H = 24, 640, 8
+    lens = torch.tensor([640, 0, 1, 127, 128, 129, 255, 256, 257, 300, 383, 384, 385, 511, 512, 513, 600, 639, 17, 64,
+                         200, 450, 77, 640], dtype=torch.int32, device="cuda")
+    q, k, v, do = make_inputs(B, T, T, H, D, dtype, std=0.5, seed=D + int(causal), requires_grad=True)
+    out = m.sigmoid_attention_padded(q, k, v, seq_lens_k=lens, seq_lens_q=lens, is_causal=causal)
+    out.backward(do)
+    qf, kf, vf = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    ref = m.sigmoid_attention_ref(qf, kf, vf, seq_lens_k=lens, seq_lens_q=lens, causal=causal)
+    valid = torch.arange(T, device="cuda")[None, :] < lens[:, None]  # [B, T]
+    ref = ref * valid[:, :, None, None]
+    ref.backward(do.float() * valid[:, :, None, None])
+    tol = {torch.float16: 2e-3, torch.bfloat16: 1e-2}[dtype]
+    assert (out.float() - ref).abs().max().item() <= tol
+    assert out[~valid].abs().max().item() == 0
+    for g, r in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        assert torch.isfinite(g).all()
+        assert g[~valid].abs().max().item() == 0
+        assert rel_l2(g[valid], r[valid]) <= 1e-2
