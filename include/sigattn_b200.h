@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define SIGATTN_ABI_VERSION 1
+#define SIGATTN_ABI_VERSION 2
 
 /* fp16 / bf16: tensor-core kernels.  fp32: exact single-precision kernels on the FMA pipe (the
  * reference accepts float32, src/triton_sigmoid/__init__.py:48, and tests it to 1e-5); they need no
@@ -81,6 +81,19 @@ typedef struct SigAttnParams {
    * kernel alone (the backward call also zero-fills and converts the dQ accumulator). */
   void *ev_main_start;
   void *ev_main_stop;
+
+  /* Packed (variable-length) layout, optional.  (No counterpart in the reference, whose padded entry
+   * point takes (B,T,H,D) tensors plus lengths; this is the layout of the flash-attention provider of
+   * its benchmark, benchmarks/benchmark_sigmoid.py:116-134.)  When both pointers are non-NULL, sequence b
+   * occupies rows cu_seqlens_q[b] .. cu_seqlens_q[b+1]-1 of q, o, dout, dq, which are (total_q, H, D),
+   * and rows cu_seqlens_k[b] .. cu_seqlens_k[b+1]-1 of k, v, dk, dv, which are (total_k, H, D).  Then B is
+   * the number of sequences, Tq / Tk are upper bounds of the sequence lengths (longer sequences are cut
+   * there), the batch strides are ignored, seq_lens_* must be NULL, score_mod is [total_k], the backward
+   * workspace is sigattn_bwd_workspace_bytes(1, total_q, H, D) bytes, and only rows of the sequences
+   * are written.  fp16 / bf16 only. */
+  const int32_t *cu_seqlens_q; /* [B+1] device, non-decreasing, cu_seqlens_q[B] <= total_q */
+  const int32_t *cu_seqlens_k; /* [B+1] device */
+  int32_t total_q, total_k;
 } SigAttnParams;
 
 /* Forward pass.  Replaces sigmoid_attention_fwd_op + _fwd_dense_kernel

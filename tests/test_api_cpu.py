@@ -13,7 +13,28 @@ def _qkv(B=2, T=32, H=2, D=64, dtype=torch.float16):
 
 
 def test_exports_match_reference_package():
-    assert set(m.__all__) == {"sigmoid_attention", "sigmoid_attention_padded", "sigmoid_attention_ref"}
+    """The reference's three names, plus the packed variable-length entry point it does not have."""
+    assert set(m.__all__) == {"sigmoid_attention", "sigmoid_attention_padded", "sigmoid_attention_ref",
+                              "sigmoid_attention_varlen"}
+
+
+def test_varlen_argument_errors():
+    q = torch.zeros(10, 2, 64, dtype=torch.float16)
+    cu = torch.tensor([0, 4, 10], dtype=torch.int32)
+    with pytest.raises(ValueError, match="3D tensors"):
+        m.sigmoid_attention_varlen(q[None], q[None], q[None], cu, cu, 6, 6)
+    with pytest.raises(ValueError, match="Key and value shapes must match"):
+        m.sigmoid_attention_varlen(q, q, q[:5], cu, cu, 6, 6)
+    with pytest.raises(ValueError, match="Number of heads mismatch"):
+        m.sigmoid_attention_varlen(q, q[:, :1], q[:, :1], cu, cu, 6, 6)
+    with pytest.raises(ValueError, match="cu_seqlens_q and cu_seqlens_k"):
+        m.sigmoid_attention_varlen(q, q, q, cu, cu[:2], 6, 6)
+    with pytest.raises(ValueError, match="score_mod must have shape"):
+        m.sigmoid_attention_varlen(q, q, q, cu, cu, 6, 6, score_mod=torch.zeros(3))
+    with pytest.raises(NotImplementedError, match="float16 or bfloat16 only"):
+        m.sigmoid_attention_varlen(q.float(), q.float(), q.float(), cu, cu, 6, 6)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        m.sigmoid_attention_varlen(q, q, q, cu, cu, 6, 6)
 
 
 @pytest.mark.parametrize("fn", [m.sigmoid_attention, m.sigmoid_attention_padded])

@@ -35,7 +35,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_query(lib):
-    assert lib.sigattn_query(_cabi.Q_ABI_VERSION) == 1
+    assert lib.sigattn_query(_cabi.Q_ABI_VERSION) == 2
     assert lib.sigattn_query(_cabi.Q_SM_ARCH) == 100
     assert lib.sigattn_query(_cabi.Q_MAX_HEAD_DIM) == 128
     assert lib.sigattn_query(_cabi.Q_PARAMS_SIZE) == ctypes.sizeof(_cabi.SigAttnParams)

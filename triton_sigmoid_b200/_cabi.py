@@ -72,6 +72,10 @@ class SigAttnParams(ctypes.Structure):
         ("stream", ctypes.c_void_p),
         ("ev_main_start", ctypes.c_void_p),
         ("ev_main_stop", ctypes.c_void_p),
+        ("cu_seqlens_q", ctypes.c_void_p),
+        ("cu_seqlens_k", ctypes.c_void_p),
+        ("total_q", ctypes.c_int32),
+        ("total_k", ctypes.c_int32),
     ]
 
 

@@ -56,6 +56,11 @@ struct BwdParams {
   int64_t dv_sb, dv_st, dv_sh;
   const int* lens_q;
   const int* lens_k;
+  // Packed (variable-length) layout: sequence b occupies rows cu_q[b] .. cu_q[b+1]-1 of a (total, H, D)
+  // tensor (likewise cu_k for keys / values); Tq, Tk are then upper bounds of the lengths and dq_acc is
+  // [total queries, H, D].  nullptr = (B, T, H, D).
+  const int* cu_q;
+  const int* cu_k;
   const float* bias;
   const float* score_mod;
   float scale;
@@ -212,6 +217,10 @@ __device__ __forceinline__ void bwd_phase_b(uint32_t dp_addr, uint32_t ds_line, 
 // One work item, decoded the same way by every warp role.
 struct BwdItem {
   int b, h, kv0;
+  int bc;               // batch coordinate of the tensor maps and strides (0 when packed)
+  int tq0, tk0;         // first row of the sequence in the token dimension (0 unless packed)
+  int key_lim;          // key rows below this exist in this sequence's tensors (Tk; packed: Lk)
+  int64_t acc_row0;     // first row of the sequence in the dQ accumulator
   int Lq, Lk;
   int i_begin, n_q;     // first query tile that sees this key tile, number of query tiles
   bool ragged_kv;       // the key tile straddles Lk
@@ -228,6 +237,19 @@ __device__ __forceinline__ BwdItem bwd_decode_item(const BwdParams& p, int item)
   it.Lk = p.Tk;
   if (p.lens_q) it.Lq = min(max(p.lens_q[it.b], 0), p.Tq);
   if (p.lens_k) it.Lk = min(max(p.lens_k[it.b], 0), p.Tk);
+  it.bc = it.b;
+  it.tq0 = it.tk0 = 0;
+  it.key_lim = p.Tk;
+  it.acc_row0 = (int64_t)it.b * p.Tq;
+  if (p.cu_q) {
+    it.tq0 = p.cu_q[it.b];
+    it.tk0 = p.cu_k[it.b];
+    it.Lq = min(max(p.cu_q[it.b + 1] - it.tq0, 0), p.Tq);
+    it.Lk = min(max(p.cu_k[it.b + 1] - it.tk0, 0), p.Tk);
+    it.bc = 0;
+    it.key_lim = it.Lk;
+    it.acc_row0 = it.tq0;
+  }
   const int i_end = (it.Lq + kBwdTileQ - 1) / kBwdTileQ;
   it.i_begin = p.causal ? j : 0;  // query tiles that can see this key tile (top-left aligned)
   it.n_q = (it.kv0 < it.Lk) ? max(i_end - it.i_begin, 0) : 0;
@@ -388,7 +410,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           mbar_expect_tx(bar(L::kQFull + st), kTileBytes);
 #pragma unroll
           for (int c = 0; c < D / 64; ++c)
-            tma_load_4d(smem_base + L::kQOff + st * kTileBytes + c * 16384, &q_map, bar(L::kQFull + st), c * 64, it.h, qrow, it.b);
+            tma_load_4d(smem_base + L::kQOff + st * kTileBytes + c * 16384, &q_map, bar(L::kQFull + st), c * 64, it.h, it.tq0 + qrow, it.bc);
         }
         ok = mbar_wait_warp(bar(L::kDoEmpty + st), ph ^ 1u, abort_flag, kSiteBase + 2);
         if (!ok) break;
@@ -396,7 +418,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           mbar_expect_tx(bar(L::kDoFull + st), kTileBytes);
 #pragma unroll
           for (int c = 0; c < D / 64; ++c)
-            tma_load_4d(smem_base + L::kDoOff + st * kTileBytes + c * 16384, &do_map, bar(L::kDoFull + st), c * 64, it.h, qrow, it.b);
+            tma_load_4d(smem_base + L::kDoOff + st * kTileBytes + c * 16384, &do_map, bar(L::kDoFull + st), c * 64, it.h, it.tq0 + qrow, it.bc);
         }
         if (t == 0) {
           // K_j, V_j of this item into buffer kb, once the products of the item that used it last have
@@ -409,8 +431,8 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
             mbar_expect_tx(bar(L::kKvFull + kb), 2 * kTileBytes);
 #pragma unroll
             for (int c = 0; c < D / 64; ++c) {
-              tma_load_4d(smem_base + L::kKOff + kb * kTileBytes + c * 16384, &k_map, bar(L::kKvFull + kb), c * 64, it.h, it.kv0, it.b);
-              tma_load_4d(smem_base + L::kVOff + kb * kTileBytes + c * 16384, &v_map, bar(L::kKvFull + kb), c * 64, it.h, it.kv0, it.b);
+              tma_load_4d(smem_base + L::kKOff + kb * kTileBytes + c * 16384, &k_map, bar(L::kKvFull + kb), c * 64, it.h, it.tk0 + it.kv0, it.bc);
+              tma_load_4d(smem_base + L::kVOff + kb * kTileBytes + c * 16384, &v_map, bar(L::kKvFull + kb), c * 64, it.h, it.tk0 + it.kv0, it.bc);
             }
           }
           if (it.ragged_kv) {
@@ -615,14 +637,17 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const BwdItem it = bwd_decode_item(p, item);
       const int b = it.b, h = it.h, kv0 = it.kv0, Lq = it.Lq, Lk = it.Lk, i_begin = it.i_begin, n_q = it.n_q;
       const int kv = kv0 + lane_row;
-      uint8_t* dk_base = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((int64_t)b * p.dk_sb + (int64_t)h * p.dk_sh);
-      uint8_t* dv_base = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((int64_t)b * p.dv_sb + (int64_t)h * p.dv_sh);
+      // row 0 of this sequence's dK / dV
+      uint8_t* dk_base = reinterpret_cast<uint8_t*>(p.dk) +
+                         2 * ((int64_t)it.bc * p.dk_sb + (int64_t)h * p.dk_sh + (int64_t)it.tk0 * p.dk_st);
+      uint8_t* dv_base = reinterpret_cast<uint8_t*>(p.dv) +
+                         2 * ((int64_t)it.bc * p.dv_sb + (int64_t)h * p.dv_sh + (int64_t)it.tk0 * p.dv_st);
       if (n_q == 0) {
         // no query sees this key tile: its gradients are zero
         constexpr int kChunksPerRow = D * 2 / 16;
         for (int i = threadIdx.x; i < kBwdTileKV * kChunksPerRow; i += kBwdComputeWarps * 32) {
           const int row = kv0 + i / kChunksPerRow;
-          if (row < p.Tk) {
+          if (row < it.key_lim) {
             *reinterpret_cast<uint4*>(dk_base + 2 * (int64_t)row * p.dk_st + 16 * (i % kChunksPerRow)) = make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4*>(dv_base + 2 * (int64_t)row * p.dv_st + 16 * (i % kChunksPerRow)) = make_uint4(0, 0, 0, 0);
           }
@@ -630,7 +655,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         continue;
       }
       float c0 = p.bias ? p.bias[b] : p.bias_scalar;
-      if (p.score_mod && kv < p.Tk) c0 += p.score_mod[(int64_t)b * p.Tk + kv];
+      if (p.score_mod && kv < it.key_lim) c0 += p.score_mod[(p.cu_k ? (int64_t)it.tk0 : (int64_t)b * p.Tk) + kv];
       c0 *= kLog2e;
       const bool row_ok = kv < Lk;
 
@@ -649,7 +674,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(gt)));  // the TMEM columns are free again
           const int q_first = q_tile + 32 * cg;
-          float* dst = p.dq_acc + (((int64_t)b * p.Tq + q_first) * p.H + h) * D + lane_row;
+          float* dst = p.dq_acc + ((it.acc_row0 + q_first) * p.H + h) * D + lane_row;
           const int64_t row_stride = (int64_t)p.H * D;
           const int n_live = min(32, Lq - q_first);  // queries at or beyond Lq get no gradient
 #pragma unroll
@@ -685,7 +710,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
             const int q = q_tile + quarter * 32 + 2 * prow + row_par;
             const uint4 w = *reinterpret_cast<const uint4*>(patch + prow * L::kDqPatchRow + chunk * 16);
             if (q < Lq) {  // queries at or beyond Lq get no gradient
-              float* dst = p.dq_acc + (((int64_t)b * p.Tq + q) * p.H + h) * D + 32 * col_half + 4 * chunk;
+              float* dst = p.dq_acc + ((it.acc_row0 + q) * p.H + h) * D + 32 * col_half + 4 * chunk;
               asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(w.x)),
                            "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
                            : "memory");
@@ -765,7 +790,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
-        if (kv < p.Tk) {
+        if (kv < it.key_lim) {
           uint8_t* out_row = (is_dk ? dk_base + 2 * (int64_t)kv * p.dk_st : dv_base + 2 * (int64_t)kv * p.dv_st) + 2 * col0;
 #pragma unroll
           for (int c = 0; c < D / 64; ++c) {

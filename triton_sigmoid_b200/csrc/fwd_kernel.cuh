@@ -34,8 +34,12 @@ struct FwdParams {
   int64_t o_sb, o_st, o_sh;  // element strides of O: batch, token, head
   const int* lens_q;
   const int* lens_k;
+  // Packed (variable-length) layout: sequence b occupies rows cu_q[b] .. cu_q[b+1]-1 of a (total, H, D)
+  // tensor (likewise cu_k for keys / values); Tq, Tk are then upper bounds of the lengths.  nullptr = (B, T, H, D).
+  const int* cu_q;
+  const int* cu_k;
   const float* bias;       // [B] or nullptr
-  const float* score_mod;  // [B, Tk] or nullptr
+  const float* score_mod;  // [B, Tk] (packed: [total keys]) or nullptr
   float scale;
   float bias_scalar;
   int B, H, Tq, Tk;
@@ -214,6 +218,10 @@ __device__ __forceinline__ void fwd_sigmoid_half_tile(uint32_t s_addr, float c1,
 // One work item, decoded the same way by every warp role.
 struct FwdItem {
   int b, h, q0;
+  int bc;             // batch coordinate of the tensor maps and strides (0 when packed)
+  int tq0, tk0;       // first row of the sequence in the token dimension (0 unless packed)
+  int row_lim;        // query rows below this are written (Tq; packed: Lq, the next rows belong to another sequence)
+  int key_lim;        // keys below this have a score_mod entry (Tk; packed: Lk)
   int Lq, Lk;
   int n0, n1, n_max;  // key tiles of query tile 0 / 1, and the larger of the two
 };
@@ -229,6 +237,19 @@ __device__ __forceinline__ FwdItem fwd_decode_item(const FwdParams& p, int item)
   it.Lk = p.Tk;
   if (p.lens_q) it.Lq = min(max(p.lens_q[it.b], 0), p.Tq);
   if (p.lens_k) it.Lk = min(max(p.lens_k[it.b], 0), p.Tk);
+  it.bc = it.b;
+  it.tq0 = it.tk0 = 0;
+  it.row_lim = p.Tq;
+  it.key_lim = p.Tk;
+  if (p.cu_q) {
+    it.tq0 = p.cu_q[it.b];
+    it.tk0 = p.cu_k[it.b];
+    it.Lq = min(max(p.cu_q[it.b + 1] - it.tq0, 0), p.Tq);
+    it.Lk = min(max(p.cu_k[it.b + 1] - it.tk0, 0), p.Tk);
+    it.bc = 0;
+    it.row_lim = it.Lq;
+    it.key_lim = it.Lk;
+  }
   int n_kv[2];
 #pragma unroll
   for (int s = 0; s < 2; ++s) {
@@ -370,7 +391,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
 #pragma unroll
             for (int c = 0; c < D / 64; ++c)
               tma_load_4d(smem_base + L::kQOff + s * kTileBytes + c * 16384, &q_map, bar(L::kQFull + s), c * 64, it.h,
-                          it.q0 + 128 * s, it.b);
+                          it.tq0 + it.q0 + 128 * s, it.bc);
           }
         }
       }
@@ -384,7 +405,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
 #pragma unroll
           for (int c = 0; c < D / 64; ++c)
             tma_load_4d(smem_base + L::kKOff + st * kTileBytes + c * 16384, &k_map, bar(L::kKFull + st), c * 64, it.h,
-                        j * kTileN, it.b);
+                        it.tk0 + j * kTileN, it.bc);
         }
         ok = mbar_wait_warp(bar(L::kVEmpty + st), ph ^ 1u, abort_flag, kSiteBase + 2);
         if (!ok) break;
@@ -393,7 +414,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
 #pragma unroll
           for (int c = 0; c < D / 64; ++c)
             tma_load_4d(smem_base + L::kVOff + st * kTileBytes + c * 16384, &v_map, bar(L::kVFull + st), c * 64, it.h,
-                        j * kTileN, it.b);
+                        it.tk0 + j * kTileN, it.bc);
         }
         if (j * kTileN + kTileN > it.Lk) {
           // The tile straddles the valid key length.  P is zero for the padded keys, but 0 * NaN
@@ -654,7 +675,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       if (!ok) break;
       const int item = item_ring[slot];
       if (item < 0) break;
-      int n0, n1, n_mine, lim, mask_from;
+      int n0, n1, n_mine, lim, mask_from, sm_lim = 0;
       float c0;
       const float* sm_row = nullptr;
       {
@@ -670,7 +691,10 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         mask_from = it.Lk;
         if (p.causal) mask_from = min(mask_from, it.q0 + 128 * s + 1);
         c0 = (p.bias ? p.bias[it.b] : p.bias_scalar) * kLog2e;
-        if constexpr (kScoreMod) sm_row = p.score_mod + (int64_t)it.b * p.Tk;
+        if constexpr (kScoreMod) {
+          sm_row = p.score_mod + (p.cu_k ? (int64_t)it.tk0 : (int64_t)it.b * p.Tk);
+          sm_lim = it.key_lim;
+        }
       }
 
       for (int j = 0; j < n_mine; ++j) {
@@ -686,9 +710,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           const int col0 = j * kTileN + 64 * (g + hh);
           // the predicate code exists only in the instantiation used by boundary tiles
           if (col0 + 64 > mask_from)
-            fwd_sigmoid_half_tile<kBF16, kScoreMod, true>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
+            fwd_sigmoid_half_tile<kBF16, kScoreMod, true>(s_addr, c1, c0, col0, lim, sm_row, sm_lim);
           else
-            fwd_sigmoid_half_tile<kBF16, kScoreMod, false>(s_addr, c1, c0, col0, lim, sm_row, p.Tk);
+            fwd_sigmoid_half_tile<kBF16, kScoreMod, false>(s_addr, c1, c0, col0, lim, sm_row, sm_lim);
         }
         tmem_st_wait();
         tc_fence_before_sync();
@@ -703,10 +727,10 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const int row = it.q0 + 128 * s + lane_row;
       // this thread's output columns (16-bit)
       uint8_t* o_row = reinterpret_cast<uint8_t*>(p.o) +
-                       2 * ((int64_t)it.b * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)row * p.o_st) + g * D;
+                       2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)(it.tq0 + row) * p.o_st) + g * D;
       if (n_mine == 0) {
         // this tile is entirely padding (or beyond Tq): zero rows
-        if (row < p.Tq) {
+        if (row < it.row_lim) {
 #pragma unroll
           for (int c = 0; c < kDMine / 8; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
         }
@@ -741,7 +765,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kOEmpty));
-        if (n_mine > 0 && row < p.Tq) {
+        if (n_mine > 0 && row < it.row_lim) {
 #pragma unroll
           for (int c = 0; c < kDMine / 32; ++c) {
 #pragma unroll

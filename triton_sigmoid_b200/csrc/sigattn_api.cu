@@ -82,6 +82,13 @@ int check_common(const SigAttnParams* p, bool backward) {
   if (p->D != 64 && p->D != 128) return fail(-2, "unsupported head dimension %d (64 or 128)", p->D);
   if (p->B < 0 || p->H < 0 || p->Tq < 0 || p->Tk < 0) return fail(-2, "negative extent");
   if (p->H > 65535 || p->B > 65535) return fail(-2, "B and H must not exceed 65535");
+  const bool packed = p->cu_seqlens_q || p->cu_seqlens_k;
+  if (packed) {
+    if (!p->cu_seqlens_q || !p->cu_seqlens_k) return fail(-1, "packed layout needs both cu_seqlens_q and cu_seqlens_k");
+    if (p->seq_lens_q || p->seq_lens_k) return fail(-2, "packed layout: seq_lens_q / seq_lens_k must be NULL");
+    if (p->dtype == SIGATTN_FP32) return fail(-2, "packed layout: fp16 / bf16 only");
+    if (p->total_q < 0 || p->total_k < 0) return fail(-2, "negative total_q / total_k");
+  }
   if (p->B == 0 || p->H == 0) return 1;  // nothing to do
   if (!p->q || !p->k || !p->v) return fail(-1, "q, k, v must not be NULL");
   if (!backward && !p->o) return fail(-1, "o must not be NULL");
@@ -91,6 +98,26 @@ int check_common(const SigAttnParams* p, bool backward) {
 
 bool is_contiguous(const int64_t* s, int T, int H, int D) {
   return s[2] == D && s[1] == (int64_t)H * D && s[0] == (int64_t)T * H * D;
+}
+
+// Extents of the tensors as the tensor maps, the accumulator and the fills see them: packed tensors are
+// one "batch" of total_q / total_k rows.
+struct Extents {
+  int B, Tq, Tk;
+  bool packed;
+};
+Extents extents(const SigAttnParams* p) {
+  const bool packed = p->cu_seqlens_q != nullptr;
+  return Extents{packed ? 1 : p->B, packed ? p->total_q : p->Tq, packed ? p->total_k : p->Tk, packed};
+}
+// {batch, token, head} strides with a usable batch stride when the tensor is packed
+struct Strides3 {
+  int64_t s[3];
+};
+Strides3 map_strides(const int64_t* strides, int T, bool packed) {
+  Strides3 r{{strides[0], strides[1], strides[2]}};
+  if (packed) r.s[0] = (int64_t)(T > 0 ? T : 1) * strides[1];
+  return r;
 }
 
 // Zero-fill a (B,T,H,D) tensor; only used for degenerate problems (no keys / no queries).
@@ -180,6 +207,8 @@ int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   fp.o_sh = p->o_strides[2];
   fp.lens_q = p->seq_lens_q;
   fp.lens_k = p->seq_lens_k;
+  fp.cu_q = p->cu_seqlens_q;
+  fp.cu_k = p->cu_seqlens_k;
   fp.bias = p->bias;
   fp.score_mod = p->score_mod;
   fp.scale = p->scale;
@@ -211,7 +240,8 @@ int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
                const CUtensorMap& dom) {
   using namespace sigattn;
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
-  const size_t need = sigattn_bwd_workspace_bytes(p->B, p->Tq, p->H, p->D);
+  const Extents ex = extents(p);
+  const size_t need = sigattn_bwd_workspace_bytes(ex.B, ex.Tq, p->H, p->D);
   if (p->workspace_bytes < need || (need && !p->workspace))
     return fail(-4, "backward workspace too small: %zu bytes given, %zu needed", p->workspace_bytes, need);
   if ((reinterpret_cast<uintptr_t>(p->workspace) & 15u) != 0) return fail(-3, "workspace must be 16-byte aligned");
@@ -226,6 +256,8 @@ int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   bp.dv_sb = p->dv_strides[0]; bp.dv_st = p->dv_strides[1]; bp.dv_sh = p->dv_strides[2];
   bp.lens_q = p->seq_lens_q;
   bp.lens_k = p->seq_lens_k;
+  bp.cu_q = p->cu_seqlens_q;
+  bp.cu_k = p->cu_seqlens_k;
   bp.bias = p->bias;
   bp.score_mod = p->score_mod;
   bp.scale = p->scale;
@@ -257,9 +289,9 @@ int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
     cp.acc = dq_acc;
     cp.dq = p->dq;
     cp.sb = p->dq_strides[0]; cp.st = p->dq_strides[1]; cp.sh = p->dq_strides[2];
-    cp.B = p->B; cp.T = p->Tq; cp.H = p->H;
+    cp.B = ex.B; cp.T = ex.Tq; cp.H = p->H;
     cp.scale = p->scale;
-    const long long chunks = (long long)p->B * p->Tq * p->H * (D / 8);
+    const long long chunks = (long long)ex.B * ex.Tq * p->H * (D / 8);
     const int threads = 256;
     const long long blocks_ll = (chunks + threads - 1) / threads;
     const int blocks = (int)(blocks_ll > 148LL * 64 ? 148LL * 64 : blocks_ll);
@@ -404,16 +436,19 @@ int sigattn_fwd(const SigAttnParams* p) {
   if (rc == 1) return 0;
   DeviceGuard g;
   SIG_CUDA(g.enter(p->device));
-  if (p->Tq == 0) return 0;
-  if (p->Tk == 0)  // no keys at all: the output is all zeros
-    return zero_fill(p->o, p->o_strides, p->B, p->Tq, p->H, p->D, p->dtype, static_cast<cudaStream_t>(p->stream), "o");
+  const Extents ex = extents(p);
+  if (ex.Tq == 0 || p->Tq == 0) return 0;
+  if (ex.Tk == 0 || p->Tk == 0) {  // no keys at all: the output is all zeros
+    const Strides3 os = map_strides(p->o_strides, ex.Tq, ex.packed);
+    return zero_fill(p->o, os.s, ex.B, ex.Tq, p->H, p->D, p->dtype, static_cast<cudaStream_t>(p->stream), "o");
+  }
   if (p->dtype == SIGATTN_FP32) return launch_f32(p, false);
   CUtensorMap qm, km, vm;
-  if ((rc = make_map(&qm, p->q, p->dtype, p->B, p->Tq, p->H, p->D, p->q_strides, 128, "q"))) return rc;
-  if ((rc = make_map(&km, p->k, p->dtype, p->B, p->Tk, p->H, p->D, p->k_strides, 128, "k"))) return rc;
-  if ((rc = make_map(&vm, p->v, p->dtype, p->B, p->Tk, p->H, p->D, p->v_strides, 128, "v"))) return rc;
+  if ((rc = make_map(&qm, p->q, p->dtype, ex.B, ex.Tq, p->H, p->D, map_strides(p->q_strides, ex.Tq, ex.packed).s, 128, "q"))) return rc;
+  if ((rc = make_map(&km, p->k, p->dtype, ex.B, ex.Tk, p->H, p->D, map_strides(p->k_strides, ex.Tk, ex.packed).s, 128, "k"))) return rc;
+  if ((rc = make_map(&vm, p->v, p->dtype, ex.B, ex.Tk, p->H, p->D, map_strides(p->v_strides, ex.Tk, ex.packed).s, 128, "v"))) return rc;
   if ((reinterpret_cast<uintptr_t>(p->o) & 15u) != 0) return fail(-3, "o: base pointer must be 16-byte aligned");
-  for (int i = 0; i < 3; ++i)
+  for (int i = ex.packed ? 1 : 0; i < 3; ++i)
     if (p->o_strides[i] % 8 != 0) return fail(-3, "o: strides must be multiples of 8 elements");
 
   const bool bf = p->dtype == SIGATTN_BF16;
@@ -437,24 +472,25 @@ int sigattn_bwd(const SigAttnParams* p) {
   if (rc == 1) return 0;
   DeviceGuard g;
   SIG_CUDA(g.enter(p->device));
-  if (p->Tq == 0 || p->Tk == 0) {
+  const Extents ex = extents(p);
+  if (ex.Tq == 0 || ex.Tk == 0 || p->Tq == 0 || p->Tk == 0) {
     // no query or no key: every gradient is zero
     cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
-    if ((rc = zero_fill(p->dq, p->dq_strides, p->B, p->Tq, p->H, p->D, p->dtype, stream, "dq"))) return rc;
-    if ((rc = zero_fill(p->dk, p->dk_strides, p->B, p->Tk, p->H, p->D, p->dtype, stream, "dk"))) return rc;
-    return zero_fill(p->dv, p->dv_strides, p->B, p->Tk, p->H, p->D, p->dtype, stream, "dv");
+    if ((rc = zero_fill(p->dq, map_strides(p->dq_strides, ex.Tq, ex.packed).s, ex.B, ex.Tq, p->H, p->D, p->dtype, stream, "dq"))) return rc;
+    if ((rc = zero_fill(p->dk, map_strides(p->dk_strides, ex.Tk, ex.packed).s, ex.B, ex.Tk, p->H, p->D, p->dtype, stream, "dk"))) return rc;
+    return zero_fill(p->dv, map_strides(p->dv_strides, ex.Tk, ex.packed).s, ex.B, ex.Tk, p->H, p->D, p->dtype, stream, "dv");
   }
   if (p->dtype == SIGATTN_FP32) return launch_f32(p, true);
   CUtensorMap qm, km, vm, dom;
-  if ((rc = make_map(&qm, p->q, p->dtype, p->B, p->Tq, p->H, p->D, p->q_strides, 128, "q"))) return rc;
-  if ((rc = make_map(&km, p->k, p->dtype, p->B, p->Tk, p->H, p->D, p->k_strides, 128, "k"))) return rc;
-  if ((rc = make_map(&vm, p->v, p->dtype, p->B, p->Tk, p->H, p->D, p->v_strides, 128, "v"))) return rc;
-  if ((rc = make_map(&dom, p->dout, p->dtype, p->B, p->Tq, p->H, p->D, p->do_strides, 128, "dout"))) return rc;
+  if ((rc = make_map(&qm, p->q, p->dtype, ex.B, ex.Tq, p->H, p->D, map_strides(p->q_strides, ex.Tq, ex.packed).s, 128, "q"))) return rc;
+  if ((rc = make_map(&km, p->k, p->dtype, ex.B, ex.Tk, p->H, p->D, map_strides(p->k_strides, ex.Tk, ex.packed).s, 128, "k"))) return rc;
+  if ((rc = make_map(&vm, p->v, p->dtype, ex.B, ex.Tk, p->H, p->D, map_strides(p->v_strides, ex.Tk, ex.packed).s, 128, "v"))) return rc;
+  if ((rc = make_map(&dom, p->dout, p->dtype, ex.B, ex.Tq, p->H, p->D, map_strides(p->do_strides, ex.Tq, ex.packed).s, 128, "dout"))) return rc;
   const void* outs[3] = {p->dq, p->dk, p->dv};
   const int64_t* ostr[3] = {p->dq_strides, p->dk_strides, p->dv_strides};
   for (int t = 0; t < 3; ++t) {
     if ((reinterpret_cast<uintptr_t>(outs[t]) & 15u) != 0) return fail(-3, "gradient pointers must be 16-byte aligned");
-    for (int i = 0; i < 3; ++i)
+    for (int i = ex.packed ? 1 : 0; i < 3; ++i)
       if (ostr[t][i] % 8 != 0) return fail(-3, "gradient strides must be multiples of 8 elements");
   }
   if (p->D == 64) return p->dtype == SIGATTN_BF16 ? launch_bwd<64, true>(p, qm, km, vm, dom) : launch_bwd<64, false>(p, qm, km, vm, dom);
@@ -466,7 +502,8 @@ int sigattn_bwd_static_scratch(const SigAttnParams* p) {
   int rc = check_common(p, true);
   if (rc < 0) return rc;
   if (rc == 1) return 0;
-  const unsigned long long elems = (unsigned long long)p->B * (unsigned long long)p->Tq * (unsigned long long)p->H *
+  const Extents ex = extents(p);
+  const unsigned long long elems = (unsigned long long)ex.B * (unsigned long long)ex.Tq * (unsigned long long)p->H *
                                    (unsigned long long)p->D;
   if (elems > SIGATTN_STATIC_SCRATCH_ELEMS)
     return fail(-4, "problem too large for the built-in scratch: B*Tq*H*D = %llu elements, limit %u; "

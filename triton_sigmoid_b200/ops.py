@@ -214,6 +214,114 @@ def _padded_backward(ctx, dO):
 sigmoid_attn_padded_fwd_op.register_autograd(_padded_backward, setup_context=_padded_setup_context)
 
 
+# ----------------------------------------------------------------------------- packed (variable-length) ops
+def _varlen_params(q, k, v, cu_q, cu_k, max_q, max_k, bias, score_mod, scale, is_causal) -> _cabi.SigAttnParams:
+    """Parameters of a call on packed (total, H, D) tensors: B = number of sequences, Tq / Tk = the
+    longest sequence, lengths and row offsets from the cumulative-length arrays."""
+    total_q, H, D = q.shape
+    p = _cabi.SigAttnParams()
+    p.struct_bytes = ctypes.sizeof(_cabi.SigAttnParams)
+    p.dtype = _DTYPE_CODE[q.dtype]
+    p.B, p.H, p.D, p.Tq, p.Tk = cu_q.numel() - 1, H, D, int(max_q), int(max_k)
+    p.flags = _cabi.SIGATTN_CAUSAL if is_causal else 0
+    p.scale = float(scale)
+    p.bias_scalar = 0.0
+    p.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    s3 = lambda t: (ctypes.c_int64 * 3)(0, t.stride(0), t.stride(1))
+    p.q_strides, p.k_strides, p.v_strides = s3(q), s3(k), s3(v)
+    p.cu_seqlens_q, p.cu_seqlens_k = cu_q.data_ptr(), cu_k.data_ptr()
+    p.total_q, p.total_k = total_q, k.shape[0]
+    p.bias = bias.data_ptr()
+    p.score_mod = score_mod.data_ptr() if score_mod is not None else None
+    p.stream = torch.cuda.current_stream(q.device).cuda_stream
+    return p
+
+
+def _check_varlen_kernel_inputs(q, k, v):
+    _require_b200(q.device)
+    if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError(f"packed sequences take float16 or bfloat16 q/k/v of one dtype, got "
+                                  f"{q.dtype}, {k.dtype}, {v.dtype}")
+    if q.shape[-1] not in (64, 128):
+        raise NotImplementedError(f"kernel head dimension must be 64 or 128, got {q.shape[-1]}")
+
+
+@torch.library.custom_op(f"{_NS}::sigmoid_attn_varlen_fwd", mutates_args=())
+def sigmoid_attn_varlen_fwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                               cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, bias: torch.Tensor,
+                               score_mod: Optional[torch.Tensor], sm_scale: float, is_causal: bool) -> torch.Tensor:
+    _check_varlen_kernel_inputs(Q, K, V)
+    Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
+    out = torch.empty_like(Q)
+    if out.numel() == 0:
+        return out
+    bias, score_mod, _, _ = _prep_aux(Q, bias, score_mod, None, None)
+    p = _varlen_params(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, bias, score_mod, sm_scale,
+                       is_causal)
+    p.o = out.data_ptr()
+    p.o_strides = (ctypes.c_int64 * 3)(0, out.stride(0), out.stride(1))
+    _cabi.check(_cabi.load().sigattn_fwd(ctypes.byref(p)), "sigattn_fwd")
+    return out
+
+
+@sigmoid_attn_varlen_fwd_op.register_fake
+def _(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, bias, score_mod, sm_scale, is_causal):
+    return torch.empty_like(Q, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op(f"{_NS}::sigmoid_attn_varlen_bwd", mutates_args=())
+def sigmoid_attn_varlen_bwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, dO: torch.Tensor,
+                               cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_q: int,
+                               max_seqlen_k: int, bias: torch.Tensor, score_mod: Optional[torch.Tensor],
+                               sm_scale: float, is_causal: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    _check_varlen_kernel_inputs(Q, K, V)
+    Q, K, V, dO = Q.contiguous(), K.contiguous(), V.contiguous(), dO.contiguous()
+    # rows between or behind the sequences (there are none when cu_seqlens covers the tensors) stay zero
+    dq, dk, dv = torch.zeros_like(Q), torch.zeros_like(K), torch.zeros_like(V)
+    if Q.numel() == 0 or K.numel() == 0:
+        return dq, dk, dv
+    bias, score_mod, _, _ = _prep_aux(Q, bias, score_mod, None, None)
+    lib = _cabi.load()
+    total_q, H, D = Q.shape
+    ws_bytes = lib.sigattn_bwd_workspace_bytes(1, total_q, H, D)
+    ws = torch.empty(max(ws_bytes, 16) // 4, dtype=torch.float32, device=Q.device)
+    p = _varlen_params(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, bias, score_mod, sm_scale,
+                       is_causal)
+    s3 = lambda t: (ctypes.c_int64 * 3)(0, t.stride(0), t.stride(1))
+    p.dout, p.do_strides = dO.data_ptr(), s3(dO)
+    p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    p.dq_strides, p.dk_strides, p.dv_strides = s3(dq), s3(dk), s3(dv)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * 4
+    _cabi.check(lib.sigattn_bwd(ctypes.byref(p)), "sigattn_bwd")
+    return dq, dk, dv
+
+
+@sigmoid_attn_varlen_bwd_op.register_fake
+def _(Q, K, V, dO, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, bias, score_mod, sm_scale, is_causal):
+    c = torch.contiguous_format
+    return (torch.empty_like(Q, memory_format=c), torch.empty_like(K, memory_format=c),
+            torch.empty_like(V, memory_format=c))
+
+
+def _varlen_setup_context(ctx, inputs, output):
+    Q, K, V, cu_q, cu_k, max_q, max_k, bias, score_mod, sm_scale, is_causal = inputs
+    ctx.save_for_backward(Q, K, V, cu_q, cu_k, bias, score_mod)
+    ctx.max_q, ctx.max_k = max_q, max_k
+    ctx.sm_scale = sm_scale
+    ctx.is_causal = is_causal
+
+
+def _varlen_backward(ctx, dO):
+    Q, K, V, cu_q, cu_k, bias, score_mod = ctx.saved_tensors
+    dQ, dK, dV = sigmoid_attn_varlen_bwd_op(Q, K, V, dO, cu_q, cu_k, ctx.max_q, ctx.max_k, bias, score_mod,
+                                            ctx.sm_scale, ctx.is_causal)
+    return dQ, dK, dV, None, None, None, None, None, None, None, None
+
+
+sigmoid_attn_varlen_fwd_op.register_autograd(_varlen_backward, setup_context=_varlen_setup_context)
+
+
 # ----------------------------------------------------------------------------- public API
 def _validate_qkv(query, key, value):
     if query.dim() != 4 or key.dim() != 4 or value.dim() != 4:
@@ -364,4 +472,69 @@ def sigmoid_attention_padded(
 
     out = sigmoid_attn_padded_fwd_op(query, key, value, seq_lens_k, seq_lens_q, bias, score_mod, float(scale),
                                      bool(is_causal))
+    return out if Dk == D else out[..., :D]
+
+
+def sigmoid_attention_varlen(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    is_causal: bool = False,
+    scale: Optional[float] = None,
+    sigmoid_bias: Optional[float] = None,
+    score_mod: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Sigmoid attention on packed variable-length sequences, differentiable in q, k, v.
+
+    ``query`` is ``[total_q, H, D]``, ``key`` / ``value`` are ``[total_k, H, D]``; sequence ``b`` owns rows
+    ``cu_seqlens_q[b] : cu_seqlens_q[b+1]`` of the query-side tensors and ``cu_seqlens_k[b] :
+    cu_seqlens_k[b+1]`` of the key-side ones (``[B+1]`` integer tensors starting at 0, as flash-attention's
+    varlen functions take them); ``max_seqlen_*`` are upper bounds of the lengths.  Each sequence is
+    computed exactly as one batch element of :func:`sigmoid_attention_padded` with those lengths
+    (default bias ``-log(length of the key sequence)``, causal mask aligned top-left, ``score_mod`` of
+    shape ``[total_k]``), but no padded tile is loaded or stored.  The reference has no such entry
+    point; its benchmark feeds this layout to the flash-attention provider it compares with.
+    float16 / bfloat16 only.
+    """
+    if query.dim() != 3 or key.dim() != 3 or value.dim() != 3:
+        raise ValueError("Expected query, key, and value to be 3D tensors [total_tokens, H, D]")
+    total_q, H, D = query.shape
+    total_k, H_k, D_k = key.shape
+    if value.shape != key.shape:
+        raise ValueError(f"Key and value shapes must match, got K={tuple(key.shape)}, V={tuple(value.shape)}")
+    if H != H_k:
+        raise ValueError(f"Number of heads mismatch: Q={H}, K={H_k}")
+    if D != D_k:
+        raise ValueError(f"Head dimension mismatch: Q={D}, K={D_k}")
+    if cu_seqlens_q.dim() != 1 or cu_seqlens_k.shape != cu_seqlens_q.shape or cu_seqlens_q.numel() < 1:
+        raise ValueError(f"cu_seqlens_q and cu_seqlens_k must be 1D of equal length B+1, got "
+                         f"{tuple(cu_seqlens_q.shape)} and {tuple(cu_seqlens_k.shape)}")
+    B = cu_seqlens_q.numel() - 1
+    if score_mod is not None:
+        if score_mod.shape != (total_k,):
+            raise ValueError(f"score_mod must have shape ({total_k},), got {score_mod.shape}")
+        score_mod = score_mod.contiguous()
+    if query.dtype == torch.float32:
+        raise NotImplementedError("packed sequences: float16 or bfloat16 only (use sigmoid_attention_padded for float32)")
+    _check_dtype(query, key, value)
+    cu_seqlens_q = cu_seqlens_q.to(device=query.device, dtype=torch.int32).contiguous()
+    cu_seqlens_k = cu_seqlens_k.to(device=query.device, dtype=torch.int32).contiguous()
+
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    Dk = _kernel_head_dim(D)
+    query, key, value = (_pad_head_dim(t, Dk).contiguous() for t in (query, key, value))
+
+    if sigmoid_bias is None:
+        lens_k = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).clamp(min=0, max=int(max_seqlen_k))
+        bias = -torch.log(lens_k.float())  # +inf for an empty key set; every probability is masked there anyway
+    else:
+        bias = torch.full((B,), float(sigmoid_bias), dtype=torch.float32, device=query.device)
+
+    out = sigmoid_attn_varlen_fwd_op(query, key, value, cu_seqlens_q, cu_seqlens_k, int(max_seqlen_q),
+                                     int(max_seqlen_k), bias, score_mod, float(scale), bool(is_causal))
     return out if Dk == D else out[..., :D]
