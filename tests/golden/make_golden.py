@@ -69,7 +69,9 @@ def run_ref(ref, q, k, v, do, lens_q, lens_k, causal, scale, bias, sm):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of MSDLLCpapers/triton-sigmoid>")
+    ref_root = sys.argv[1]
     ref = load_reference(ref_root)
     torch.set_num_threads(1)
 
