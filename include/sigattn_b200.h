@@ -143,8 +143,11 @@ const char *sigattn_last_error(void);
 int sigattn_query(int what);
 
 /* Device-side health word of `device`: 0 = no kernel of this library has given up on a
- * bounded wait since the last call; otherwise a code identifying the wait.  Synchronises
- * the device.  Negative = CUDA error (see sigattn_last_error). */
+ * bounded wait since the last call; otherwise a code identifying the wait (the results of
+ * launches since the last call are then undefined; while the word is set further launches
+ * do nothing).  Reading a non-zero word clears it and the kernels' work-item counters, so
+ * the library can be used again.  Synchronises the device.  Negative = CUDA error (see
+ * sigattn_last_error). */
 int sigattn_device_status(int device);
 
 #ifdef __cplusplus

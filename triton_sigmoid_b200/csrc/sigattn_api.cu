@@ -422,8 +422,13 @@ int sigattn_device_status(int device) {
   int v = 0;
   SIG_CUDA(cudaMemcpyFromSymbol(&v, sigattn::g_status_word, sizeof(int)));
   if (v != 0) {
+    // A kernel that gave up may have left its work-item counters half used: clear them together
+    // with the status, so that the library is usable again after the caller has seen the failure.
     int zero = 0;
     SIG_CUDA(cudaMemcpyToSymbol(sigattn::g_status_word, &zero, sizeof(int)));
+    void* tickets = nullptr;
+    SIG_CUDA(cudaGetSymbolAddress(&tickets, g_item_tickets));
+    SIG_CUDA(cudaMemset(tickets, 0, sizeof(unsigned int) * 2 * kTicketSlots));
   }
   return v;
 }
