@@ -150,6 +150,14 @@ int sigattn_query(int what);
  * sigattn_last_error). */
 int sigattn_device_status(int device);
 
+/* Diagnostic (no counterpart in the reference): launches a one-warp kernel that waits, with a limit
+ * of `limit_ms` milliseconds (1..1000), on a barrier nothing arrives on, the way a kernel of this
+ * library would wait for a lost signal.  Returns 1 when the wait gave up in an orderly way (the
+ * expected outcome; the health word of the device is then set, see sigattn_device_status), 0 if
+ * it did not, negative on a CUDA error.  Allocates 4 bytes of device memory for the duration of
+ * the call and synchronises the device. */
+int sigattn_selftest_bounded_wait(int device, int limit_ms);
+
 #ifdef __cplusplus
 }
 #endif

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "sigattn_last_error",
     "sigattn_query",
     "sigattn_device_status",
+    "sigattn_selftest_bounded_wait",
 )
 
 
@@ -112,6 +113,8 @@ def load() -> ctypes.CDLL:
         lib.sigattn_query.restype = ctypes.c_int
         lib.sigattn_device_status.argtypes = [ctypes.c_int]
         lib.sigattn_device_status.restype = ctypes.c_int
+        lib.sigattn_selftest_bounded_wait.argtypes = [ctypes.c_int, ctypes.c_int]
+        lib.sigattn_selftest_bounded_wait.restype = ctypes.c_int
         if lib.sigattn_query(Q_PARAMS_SIZE) != ctypes.sizeof(SigAttnParams):
             raise ImportError(
                 f"SigAttnParams layout mismatch: library {lib.sigattn_query(Q_PARAMS_SIZE)} bytes, "

@@ -54,14 +54,15 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Bounded wait.  Returns false when the wait was abandoned, either because this thread
 // ran out of time (it then raises *abort_flag and records `site` in the health word) or
 // because another thread of the CTA already did.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(&g_status_word, 0, site);
         return false;

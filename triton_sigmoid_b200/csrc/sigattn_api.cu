@@ -394,6 +394,24 @@ int launch_f32(const SigAttnParams* p, bool backward) {
   return p->D == 64 ? launch_f32_d<64>(p, backward) : launch_f32_d<128>(p, backward);
 }
 
+// Self-test of the bounded waits: one warp waits on a barrier that nothing ever arrives on, with a
+// limit of a few milliseconds, exactly as a kernel of the library would on a lost signal: the wait
+// gives up, records its site in the health word, and the kernel returns normally.
+constexpr int kSelfTestSite = 0x30001;
+__global__ void sigattn_selftest_wait_kernel(unsigned long long limit_ns, int* gave_up) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  __shared__ int abort_flag;
+  const uint32_t bar = sigattn::smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    sigattn::mbar_init(bar, 1);
+    sigattn::fence_mbar_init();
+  }
+  __syncthreads();
+  const bool ok = sigattn::mbar_wait(bar, 0, &abort_flag, kSelfTestSite, limit_ns);
+  if (threadIdx.x == 0) *gave_up = ok ? 0 : 1;
+}
+
 }  // namespace
 
 extern "C" {
@@ -433,6 +451,25 @@ int sigattn_device_status(int device) {
   return v;
 }
 
+
+int sigattn_selftest_bounded_wait(int device, int limit_ms) {
+  g_err[0] = 0;
+  if (limit_ms < 1 || limit_ms > 1000) return fail(-2, "limit_ms must be in [1, 1000], got %d", limit_ms);
+  DeviceGuard g;
+  SIG_CUDA(g.enter(device));
+  int* flag = nullptr;
+  SIG_CUDA(cudaMalloc(&flag, sizeof(int)));
+  cudaError_t e = cudaMemset(flag, 0xff, sizeof(int));
+  int gave_up = -1;
+  if (e == cudaSuccess) {
+    sigattn_selftest_wait_kernel<<<1, 32>>>((unsigned long long)limit_ms * 1000000ull, flag);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(&gave_up, flag, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaFree(flag);
+  if (e != cudaSuccess) return fail(-100, "self-test: %s", cudaGetErrorString(e));
+  return gave_up;
+}
 
 int sigattn_fwd(const SigAttnParams* p) {
   g_err[0] = 0;
