@@ -89,8 +89,8 @@ typedef struct SigAttnParams {
    * and rows cu_seqlens_k[b] .. cu_seqlens_k[b+1]-1 of k, v, dk, dv, which are (total_k, H, D).  Then B is
    * the number of sequences, Tq / Tk are upper bounds of the sequence lengths (longer sequences are cut
    * there), the batch strides are ignored, seq_lens_* must be NULL, score_mod is [total_k], the backward
-   * workspace is sigattn_bwd_workspace_bytes(1, total_q, H, D) bytes, and only rows of the sequences
-   * are written.  fp16 / bf16 only. */
+   * workspace is sigattn_bwd_workspace_bytes(1, total_q, H, D) bytes (none for fp32), and only rows of
+   * the sequences are written. */
   const int32_t *cu_seqlens_q; /* [B+1] device, non-decreasing, cu_seqlens_q[B] <= total_q */
   const int32_t *cu_seqlens_k; /* [B+1] device */
   int32_t total_q, total_k;

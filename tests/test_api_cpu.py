@@ -31,8 +31,8 @@ def test_varlen_argument_errors():
         m.sigmoid_attention_varlen(q, q, q, cu, cu[:2], 6, 6)
     with pytest.raises(ValueError, match="score_mod must have shape"):
         m.sigmoid_attention_varlen(q, q, q, cu, cu, 6, 6, score_mod=torch.zeros(3))
-    with pytest.raises(NotImplementedError, match="float16 or bfloat16 only"):
-        m.sigmoid_attention_varlen(q.float(), q.float(), q.float(), cu, cu, 6, 6)
+    with pytest.raises(NotImplementedError, match="float64"):
+        m.sigmoid_attention_varlen(q.double(), q.double(), q.double(), cu, cu, 6, 6)
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         m.sigmoid_attention_varlen(q, q, q, cu, cu, 6, 6)
 

@@ -112,3 +112,26 @@ def test_many_sequences_many_items():
     assert torch.equal(out, pack(ref.detach()))
     assert torch.equal(k.grad, pack(kp.grad)) and torch.equal(v.grad, pack(vp.grad))
     assert rel_l2(q.grad, pack(qp.grad)) <= 1e-3  # dQ: same terms, reduction order differs
+
+
+def test_float32_sequences():
+    """float32 takes the exact kernels: same gate as the dense float32 tests (1e-5 against the float64 oracle)."""
+    lens_q, lens_k = [70, 0, 129, 33], [70, 20, 200, 64]
+    q, k, v, do, cu_q, cu_k = _packed(lens_q, lens_k, 2, 64, torch.float32, seed=8)
+    for t in (q, k, v):
+        t.requires_grad_()
+    out = m.sigmoid_attention_varlen(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k))
+    out.backward(do)
+    oq = ok = 0
+    for lq, lk in zip(lens_q, lens_k):
+        sq, sk = slice(oq, oq + lq), slice(ok, ok + lk)
+        oq, ok = oq + lq, ok + lk
+        if lq == 0:
+            assert k.grad[sk].abs().max().item() == 0
+            continue
+        args = [t[s][None] for t, s in ((q, sq), (k, sk), (v, sk))]
+        ref = orc.sigattn_forward(*args, work=torch.float64)[0]
+        assert (out[sq].detach().double().cpu() - ref).abs().max().item() <= 1e-5
+        rd = orc.sigattn_backward(*args, do[sq][None], work=torch.float64)
+        for g, r in ((q.grad[sq], rd[0][0]), (k.grad[sk], rd[1][0]), (v.grad[sk], rd[2][0])):
+            assert rel_l2(g.double().cpu(), r) <= 1e-5

@@ -28,8 +28,12 @@ struct F32Params {
   int64_t do_sb, do_st, do_sh, dq_sb, dq_st, dq_sh, dk_sb, dk_st, dk_sh, dv_sb, dv_st, dv_sh;
   const int* lens_q;
   const int* lens_k;
+  // packed layout: sequence b = rows cu_q[b] .. cu_q[b+1]-1 of (total, H, D) tensors (cu_k for keys / values),
+  // Tq / Tk upper bounds of the lengths; nullptr = (B, T, H, D)
+  const int* cu_q;
+  const int* cu_k;
   const float* bias;       // [B] or nullptr
-  const float* score_mod;  // [B, Tk] or nullptr
+  const float* score_mod;  // [B, Tk] (packed: [total keys]) or nullptr
   float scale;
   float bias_scalar;
   int B, H, Tq, Tk;
@@ -114,6 +118,11 @@ __device__ __forceinline__ float f32_sigmoid(float x) { return 1.0f / (1.0f + ex
 
 struct F32Item {
   int b, h, Lq, Lk;
+  int bc;            // batch coordinate for the strides (0 when packed)
+  int tq0, tk0;      // first row of the sequence in the token dimension (0 unless packed)
+  int row_lim;       // query rows below this are written (Tq; packed: Lq)
+  int key_lim;       // key rows below this are written / have a score_mod entry (Tk; packed: Lk)
+  int64_t sm_off;    // offset of the sequence's first key in score_mod
 };
 __device__ __forceinline__ F32Item f32_item(const F32Params& p) {
   F32Item it;
@@ -123,6 +132,21 @@ __device__ __forceinline__ F32Item f32_item(const F32Params& p) {
   it.Lk = p.Tk;
   if (p.lens_q) it.Lq = min(max(p.lens_q[it.b], 0), p.Tq);
   if (p.lens_k) it.Lk = min(max(p.lens_k[it.b], 0), p.Tk);
+  it.bc = it.b;
+  it.tq0 = it.tk0 = 0;
+  it.row_lim = p.Tq;
+  it.key_lim = p.Tk;
+  it.sm_off = (int64_t)it.b * p.Tk;
+  if (p.cu_q) {
+    it.tq0 = p.cu_q[it.b];
+    it.tk0 = p.cu_k[it.b];
+    it.Lq = min(max(p.cu_q[it.b + 1] - it.tq0, 0), p.Tq);
+    it.Lk = min(max(p.cu_k[it.b + 1] - it.tk0, 0), p.Tk);
+    it.bc = 0;
+    it.row_lim = it.Lq;
+    it.key_lim = it.Lk;
+    it.sm_off = it.tk0;
+  }
   return it;
 }
 
@@ -138,11 +162,11 @@ __global__ void __launch_bounds__(kF32Threads) sigattn_fwd_f32_kernel(const F32P
   const F32Item it = f32_item(p);
   const int q0 = blockIdx.x * kF32Tile;
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
-  const float* qb = p.q + (int64_t)it.b * p.q_sb + (int64_t)it.h * p.q_sh;
-  const float* kb = p.k + (int64_t)it.b * p.k_sb + (int64_t)it.h * p.k_sh;
-  const float* vb = p.v + (int64_t)it.b * p.v_sb + (int64_t)it.h * p.v_sh;
+  const float* qb = p.q + (int64_t)it.bc * p.q_sb + (int64_t)it.h * p.q_sh + (int64_t)it.tq0 * p.q_st;
+  const float* kb = p.k + (int64_t)it.bc * p.k_sb + (int64_t)it.h * p.k_sh + (int64_t)it.tk0 * p.k_st;
+  const float* vb = p.v + (int64_t)it.bc * p.v_sb + (int64_t)it.h * p.v_sh + (int64_t)it.tk0 * p.v_st;
   const float bias = p.bias ? p.bias[it.b] : p.bias_scalar;
-  const float* sm = p.score_mod ? p.score_mod + (int64_t)it.b * p.Tk : nullptr;
+  const float* sm = p.score_mod ? p.score_mod + it.sm_off : nullptr;
 
   float o[4][D / 16];
 #pragma unroll
@@ -167,17 +191,17 @@ __global__ void __launch_bounds__(kF32Threads) sigattn_fwd_f32_kernel(const F32P
         const int i = q0 + ty + 16 * a, j = k0 + tx + 16 * c;
         const bool visible = i < it.Lq && j < it.Lk && (!p.causal || j <= i);
         float x = s[a][c] * p.scale + bias;
-        if (sm && j < p.Tk) x += sm[j];
+        if (sm && j < it.key_lim) x += sm[j];
         Ps[(ty + 16 * a) * L::kPRow + tx + 16 * c] = visible ? f32_sigmoid(x) : 0.f;
       }
     __syncthreads();
     f32_accumulate<D, false>(Ps, Vs, ty, tx, o);
   }
-  float* ob = p.o + (int64_t)it.b * p.o_sb + (int64_t)it.h * p.o_sh;
+  float* ob = p.o + (int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)it.tq0 * p.o_st;
 #pragma unroll
   for (int a = 0; a < 4; ++a) {
     const int i = q0 + ty + 16 * a;
-    if (i < p.Tq) {
+    if (i < it.row_lim) {
 #pragma unroll
       for (int c = 0; c < D / 16; ++c) ob[(int64_t)i * p.o_st + tx + 16 * c] = (i < it.Lq) ? o[a][c] : 0.f;
     }
@@ -201,7 +225,7 @@ __device__ __forceinline__ void f32_p_and_ds(const F32Params& p, const F32Item& 
       const int i = q0 + ty + 16 * a, j = k0 + tx + 16 * c;
       const bool visible = i < it.Lq && j < it.Lk && (!p.causal || j <= i);
       float x = s[a][c] * p.scale + bias;
-      if (sm && j < p.Tk) x += sm[j];
+      if (sm && j < it.key_lim) x += sm[j];
       const float pr = visible ? f32_sigmoid(x) : 0.f;
       if (Ps) Ps[(ty + 16 * a) * L::kPRow + tx + 16 * c] = pr;
       dSs[(ty + 16 * a) * L::kPRow + tx + 16 * c] = visible ? pr * (1.0f - pr) * dp[a][c] : 0.f;
@@ -222,12 +246,12 @@ __global__ void __launch_bounds__(kF32Threads) sigattn_bwd_dkdv_f32_kernel(const
   const F32Item it = f32_item(p);
   const int k0 = blockIdx.x * kF32Tile;
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
-  const float* qb = p.q + (int64_t)it.b * p.q_sb + (int64_t)it.h * p.q_sh;
-  const float* kb = p.k + (int64_t)it.b * p.k_sb + (int64_t)it.h * p.k_sh;
-  const float* vb = p.v + (int64_t)it.b * p.v_sb + (int64_t)it.h * p.v_sh;
-  const float* dob = p.dout + (int64_t)it.b * p.do_sb + (int64_t)it.h * p.do_sh;
+  const float* qb = p.q + (int64_t)it.bc * p.q_sb + (int64_t)it.h * p.q_sh + (int64_t)it.tq0 * p.q_st;
+  const float* kb = p.k + (int64_t)it.bc * p.k_sb + (int64_t)it.h * p.k_sh + (int64_t)it.tk0 * p.k_st;
+  const float* vb = p.v + (int64_t)it.bc * p.v_sb + (int64_t)it.h * p.v_sh + (int64_t)it.tk0 * p.v_st;
+  const float* dob = p.dout + (int64_t)it.bc * p.do_sb + (int64_t)it.h * p.do_sh + (int64_t)it.tq0 * p.do_st;
   const float bias = p.bias ? p.bias[it.b] : p.bias_scalar;
-  const float* sm = p.score_mod ? p.score_mod + (int64_t)it.b * p.Tk : nullptr;
+  const float* sm = p.score_mod ? p.score_mod + it.sm_off : nullptr;
 
   float dk[4][D / 16], dv[4][D / 16];
 #pragma unroll
@@ -251,12 +275,12 @@ __global__ void __launch_bounds__(kF32Threads) sigattn_bwd_dkdv_f32_kernel(const
     f32_accumulate<D, true>(Ps, dOs, ty, tx, dv);
     f32_accumulate<D, true>(dSs, Qs, ty, tx, dk);
   }
-  float* dkb = p.dk + (int64_t)it.b * p.dk_sb + (int64_t)it.h * p.dk_sh;
-  float* dvb = p.dv + (int64_t)it.b * p.dv_sb + (int64_t)it.h * p.dv_sh;
+  float* dkb = p.dk + (int64_t)it.bc * p.dk_sb + (int64_t)it.h * p.dk_sh + (int64_t)it.tk0 * p.dk_st;
+  float* dvb = p.dv + (int64_t)it.bc * p.dv_sb + (int64_t)it.h * p.dv_sh + (int64_t)it.tk0 * p.dv_st;
 #pragma unroll
   for (int a = 0; a < 4; ++a) {
     const int j = k0 + ty + 16 * a;
-    if (j < p.Tk) {
+    if (j < it.key_lim) {
       const bool live = j < it.Lk;
 #pragma unroll
       for (int c = 0; c < D / 16; ++c) {
@@ -280,12 +304,12 @@ __global__ void __launch_bounds__(kF32Threads) sigattn_bwd_dq_f32_kernel(const F
   const F32Item it = f32_item(p);
   const int q0 = blockIdx.x * kF32Tile;
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
-  const float* qb = p.q + (int64_t)it.b * p.q_sb + (int64_t)it.h * p.q_sh;
-  const float* kb = p.k + (int64_t)it.b * p.k_sb + (int64_t)it.h * p.k_sh;
-  const float* vb = p.v + (int64_t)it.b * p.v_sb + (int64_t)it.h * p.v_sh;
-  const float* dob = p.dout + (int64_t)it.b * p.do_sb + (int64_t)it.h * p.do_sh;
+  const float* qb = p.q + (int64_t)it.bc * p.q_sb + (int64_t)it.h * p.q_sh + (int64_t)it.tq0 * p.q_st;
+  const float* kb = p.k + (int64_t)it.bc * p.k_sb + (int64_t)it.h * p.k_sh + (int64_t)it.tk0 * p.k_st;
+  const float* vb = p.v + (int64_t)it.bc * p.v_sb + (int64_t)it.h * p.v_sh + (int64_t)it.tk0 * p.v_st;
+  const float* dob = p.dout + (int64_t)it.bc * p.do_sb + (int64_t)it.h * p.do_sh + (int64_t)it.tq0 * p.do_st;
   const float bias = p.bias ? p.bias[it.b] : p.bias_scalar;
-  const float* sm = p.score_mod ? p.score_mod + (int64_t)it.b * p.Tk : nullptr;
+  const float* sm = p.score_mod ? p.score_mod + it.sm_off : nullptr;
 
   float dq[4][D / 16];
 #pragma unroll
@@ -308,11 +332,11 @@ __global__ void __launch_bounds__(kF32Threads) sigattn_bwd_dq_f32_kernel(const F
     __syncthreads();
     f32_accumulate<D, false>(dSs, Ks, ty, tx, dq);
   }
-  float* dqb = p.dq + (int64_t)it.b * p.dq_sb + (int64_t)it.h * p.dq_sh;
+  float* dqb = p.dq + (int64_t)it.bc * p.dq_sb + (int64_t)it.h * p.dq_sh + (int64_t)it.tq0 * p.dq_st;
 #pragma unroll
   for (int a = 0; a < 4; ++a) {
     const int i = q0 + ty + 16 * a;
-    if (i < p.Tq) {
+    if (i < it.row_lim) {
 #pragma unroll
       for (int c = 0; c < D / 16; ++c) dqb[(int64_t)i * p.dq_st + tx + 16 * c] = (i < it.Lq) ? dq[a][c] * p.scale : 0.f;
     }

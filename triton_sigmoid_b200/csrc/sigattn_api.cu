@@ -86,7 +86,6 @@ int check_common(const SigAttnParams* p, bool backward) {
   if (packed) {
     if (!p->cu_seqlens_q || !p->cu_seqlens_k) return fail(-1, "packed layout needs both cu_seqlens_q and cu_seqlens_k");
     if (p->seq_lens_q || p->seq_lens_k) return fail(-2, "packed layout: seq_lens_q / seq_lens_k must be NULL");
-    if (p->dtype == SIGATTN_FP32) return fail(-2, "packed layout: fp16 / bf16 only");
     if (p->total_q < 0 || p->total_k < 0) return fail(-2, "negative total_q / total_k");
   }
   if (p->B == 0 || p->H == 0) return 1;  // nothing to do
@@ -349,6 +348,8 @@ int launch_f32_d(const SigAttnParams* p, bool backward) {
   fp.dv_sb = p->dv_strides[0]; fp.dv_st = p->dv_strides[1]; fp.dv_sh = p->dv_strides[2];
   fp.lens_q = p->seq_lens_q;
   fp.lens_k = p->seq_lens_k;
+  fp.cu_q = p->cu_seqlens_q;
+  fp.cu_k = p->cu_seqlens_k;
   fp.bias = p->bias;
   fp.score_mod = p->score_mod;
   fp.scale = p->scale;

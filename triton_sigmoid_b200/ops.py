@@ -240,8 +240,8 @@ def _varlen_params(q, k, v, cu_q, cu_k, max_q, max_k, bias, score_mod, scale, is
 
 def _check_varlen_kernel_inputs(q, k, v):
     _require_b200(q.device)
-    if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
-        raise NotImplementedError(f"packed sequences take float16 or bfloat16 q/k/v of one dtype, got "
+    if q.dtype not in _SUPPORTED_DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError(f"packed sequences take float16, bfloat16 or float32 q/k/v of one dtype, got "
                                   f"{q.dtype}, {k.dtype}, {v.dtype}")
     if q.shape[-1] not in (64, 128):
         raise NotImplementedError(f"kernel head dimension must be 64 or 128, got {q.shape[-1]}")
@@ -498,7 +498,6 @@ def sigmoid_attention_varlen(
     (default bias ``-log(length of the key sequence)``, causal mask aligned top-left, ``score_mod`` of
     shape ``[total_k]``), but no padded tile is loaded or stored.  The reference has no such entry
     point; its benchmark feeds this layout to the flash-attention provider it compares with.
-    float16 / bfloat16 only.
     """
     if query.dim() != 3 or key.dim() != 3 or value.dim() != 3:
         raise ValueError("Expected query, key, and value to be 3D tensors [total_tokens, H, D]")
@@ -518,8 +517,6 @@ def sigmoid_attention_varlen(
         if score_mod.shape != (total_k,):
             raise ValueError(f"score_mod must have shape ({total_k},), got {score_mod.shape}")
         score_mod = score_mod.contiguous()
-    if query.dtype == torch.float32:
-        raise NotImplementedError("packed sequences: float16 or bfloat16 only (use sigmoid_attention_padded for float32)")
     _check_dtype(query, key, value)
     cu_seqlens_q = cu_seqlens_q.to(device=query.device, dtype=torch.int32).contiguous()
     cu_seqlens_k = cu_seqlens_k.to(device=query.device, dtype=torch.int32).contiguous()
