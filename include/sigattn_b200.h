@@ -16,9 +16,8 @@
  *    must be 16-byte aligned and every stride times the element size a multiple of 16 bytes.
  *  - The tensor-core kernels are persistent (one CTA per SM draws work items from a counter).  Each
  *    launch takes the next of 1024 counter pairs built into the library's device image and leaves it
- *    at zero when it ends, so up to 1024 launches may be in flight per device at a time; a launch
- *    captured into a CUDA graph keeps the pair it was captured with, so replays of one graph must
- *    not overlap each other (which stream order already guarantees for one executable graph).
+ *    at zero when it ends (the pair is chosen on the host when the call is made), so up to 1024
+ *    launches may be in flight per device at a time.
  *  - Return value 0 = launched; negative = rejected before any launch, with a message
  *    available from sigattn_last_error() on the calling thread.
  *  - Supported: dtype fp16 / bf16 / fp32, D in {64, 128}, 1 <= H, B, Tq, Tk (zero-sized problems
