@@ -70,6 +70,9 @@ def test_null_params_rejected(lib):
     (dict(H=70000), b"65535"),
     (dict(q=None), b"must not be NULL"),
     (dict(o=None), b"o must not be NULL"),
+    (dict(cu_seqlens_q=0x2000), b"needs both cu_seqlens_q and cu_seqlens_k"),
+    (dict(cu_seqlens_q=0x2000, cu_seqlens_k=0x2000, seq_lens_k=0x3000), b"seq_lens_q / seq_lens_k must be NULL"),
+    (dict(cu_seqlens_q=0x2000, cu_seqlens_k=0x2000, total_q=-1), b"negative total_q"),
 ])
 def test_bad_arguments_rejected_before_any_cuda_call(lib, kw, needle):
     rc = lib.sigattn_fwd(ctypes.byref(_params(**kw)))
