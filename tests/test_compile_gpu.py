@@ -57,3 +57,20 @@ def test_opcheck():
     bias = torch.zeros(1, device="cuda")
     torch.library.opcheck(ops.sigmoid_attention_fwd_op, (q, k, v, bias, None, 0.125, True),
                           test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+
+
+def test_varlen_compiled_matches_eager():
+    lens = [100, 260, 31]
+    cu = torch.tensor([0, 100, 360, 391], dtype=torch.int32, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(7)
+    q, k, v, do = [(torch.randn(391, 2, 64, device="cuda", generator=g) * 0.5).half() for _ in range(4)]
+    for t in (q, k, v):
+        t.requires_grad_()
+    fn = _compile(lambda q, k, v, cu: m.sigmoid_attention_varlen(q, k, v, cu, cu, max(lens), max(lens), is_causal=True))
+    out = fn(q, k, v, cu)
+    out.backward(do)
+    gk = k.grad.clone()
+    q.grad = k.grad = v.grad = None
+    ref = m.sigmoid_attention_varlen(q, k, v, cu, cu, max(lens), max(lens), is_causal=True)
+    ref.backward(do)
+    assert torch.equal(out, ref) and torch.equal(gk, k.grad)
