@@ -72,8 +72,8 @@ def peaks():
         with open(path) as f:
             pk = json.load(f)
         return dict(burst=float(pk["bf16_tflops"]), sustained=float(pk.get("bf16_tflops_sustained", pk["bf16_tflops"])),
-                    source="measured")
-    return dict(burst=1590.0, sustained=1400.0, source="fallback")
+                    hbm_gbs=float(pk.get("hbm_gbs", 6650.0)), source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm_gbs=6650.0, source="fallback")
 
 
 class ClockSampler:
@@ -422,7 +422,12 @@ def main():
                             "algorithmic_bytes": 14.0 * elems,
                             "peak_source": f"{pk['source']} bf16 cuBLAS burst", "ms_per_launch": kb,
                             "fwd_kernel": {"traffic": traffic_fwd, "algorithmic_bytes": 8.0 * elems, "achieved": F / (kf * 1e-3) / 1e12, "frac": F / (kf * 1e-3) / 1e12 / pk["burst"],
-                                           "ms_per_launch": kf}}
+                                           "ms_per_launch": kf},
+                            # the same launches against the HBM roof (short sequences come near it: the
+                            # arithmetic intensity of the forward is N/2 FLOP per byte)
+                            "hbm": {"bwd_gbs": 14.0 * elems / (kb * 1e-3) / 1e9, "fwd_gbs": 8.0 * elems / (kf * 1e-3) / 1e9,
+                                    "peak_gbs": pk["hbm_gbs"], "bwd_frac": 14.0 * elems / (kb * 1e-3) / 1e9 / pk["hbm_gbs"],
+                                    "fwd_frac": 8.0 * elems / (kf * 1e-3) / 1e9 / pk["hbm_gbs"]}}
         # kernels of this library per timed step: forward, backward, dQ convert
         line["gpu_launches"] = 3 * args.steps
         if rank == 0 and world == 1 and not args.no_cpu_baseline:
