@@ -64,6 +64,7 @@ constexpr int kFwdIssuerWarp = kFwdSigmoidWarps + 1;   // S = Q K^T, owns the TM
 constexpr int kFwdIssuerWarp2 = kFwdSigmoidWarps + 2;  // O += P V
 constexpr int kFwdThreads = (kFwdSigmoidWarps + 4) * 32;  // the role warps form a register-allocation group of four
 constexpr int kFwdLaunchRegs = 96;  // what 640 threads per CTA get each: 65536 / 640, rounded down to a multiple of 8
+static_assert(kFwdThreads == 640, "the register re-allocation below is worked out for 20 warps (SIG_FWD_HALVES = 2)");
 // Registers per thread after the re-allocation: the role warps (a group of four) and the sigmoid warps.
 // D = 64: the role warps fit in 32; D = 128: the single issuing warp carries two job cursors.
 template <int D> struct FwdRegs {
