@@ -93,12 +93,12 @@ struct FwdSmem {
   static constexpr int kVEmpty = kVFull + kStages;    // [kStages]
   static constexpr int kSFull = kVEmpty + kStages;    // [kSBufs]
   static constexpr int kPFull = kSFull + kSBufs;      // [kSBufs]
-  static constexpr int kOFull = kPFull + kSBufs;      // [2] per query tile: its last P V product of the item is complete
-  static constexpr int kVFix = kOFull + 2;            // [kStages] padded rows of the stage's V tile zeroed
+  static constexpr int kOFull = kPFull + kSBufs;      // [1]
+  static constexpr int kVFix = kOFull + 1;            // [kStages] padded rows of the stage's V tile zeroed
   static constexpr int kPvDone = kVFix + kStages;     // [kSBufs] P V product of the buffer's job complete
   static constexpr int kQEmpty = kPvDone + kSBufs;    // [1] all score products of the item issued and complete
-  static constexpr int kOEmpty = kQEmpty + 1;         // [2] per query tile: its O of the item read out of TMEM
-  static constexpr int kItemFull = kOEmpty + 2;       // [2] item index published
+  static constexpr int kOEmpty = kQEmpty + 1;         // [1] O of the item read out of TMEM
+  static constexpr int kItemFull = kOEmpty + 1;       // [2] item index published
   static constexpr int kItemEmpty = kItemFull + 2;    // [2] item index read by every consumer warp
   static constexpr int kNumBars = kItemEmpty + 2;
   static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int), item ring (2 int)
@@ -315,12 +315,10 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       mbar_init(bar(L::kPFull + i), 4 * kFwdHalves);  // one arrival per sigmoid warp of the query tile
       mbar_init(bar(L::kPvDone + i), 1);
     }
-    mbar_init(bar(L::kOFull + 0), 1);
-    mbar_init(bar(L::kOFull + 1), 1);
+    mbar_init(bar(L::kOFull), 1);
     for (int i = 0; i < kStages; ++i) mbar_init(bar(L::kVFix + i), 1);
     mbar_init(bar(L::kQEmpty), 1);
-    mbar_init(bar(L::kOEmpty + 0), 4 * kFwdHalves);  // the sigmoid warps of one query tile
-    mbar_init(bar(L::kOEmpty + 1), 4 * kFwdHalves);
+    mbar_init(bar(L::kOEmpty), kFwdSigmoidWarps);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(L::kItemFull + i), 1);
       mbar_init(bar(L::kItemEmpty + i), kItemReaders);
@@ -521,7 +519,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       FwdCursor cp = cs;                       // next P V product to issue
       uint32_t q_par0 = 0u, q_par1 = 0u;       // parity of each Q tile's "full" barrier
       uint32_t fix_par = 0u;                   // bit st: parity of stage st's "padded V rows cleared" barrier
-      int o_cnt0 = 0, o_cnt1 = 0;              // items in which query tile 0 / 1 had work so far
+      int act = 0;                             // items with work so far
       int n0 = 0, n1 = 0, Lk = 0;
 
       // S[buf] = Q_s K_j^T
@@ -543,12 +541,6 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       };
       // O_s += P[buf] V_j
       auto issue_pv = [&](const FwdCursor& c) {
-        if (c.j == 0) {
-          // the accumulator of this query tile still holds its O of an earlier item until the tile's
-          // sigmoid warps have read it
-          const int uses = c.s ? o_cnt1 : o_cnt0;
-          if (uses > 0) ok = ok && mbar_wait_warp(bar(L::kOEmpty + c.s), (uint32_t)(uses - 1) & 1u, abort_flag, kSiteBase + 33);
-        }
         if (c.fresh) {
           ok = ok && mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
           if (c.j * kTileN + kTileN > Lk) {  // padded V rows are being cleared by the producer warp
@@ -570,10 +562,6 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
                  kk > 0 ? 1u : acc0);
         }
         if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
-        if (c.j == (c.s ? n1 : n0) - 1) {  // the tile's last product of the item: its O is complete
-          mma_commit(leader, bar(L::kOFull + c.s));
-          if (c.s) ++o_cnt1; else ++o_cnt0;
-        }
       };
 
       for (int k = 0; ok; ++k) {
@@ -596,14 +584,18 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           if (++n_s == n_jobs && ok) mma_commit(leader, bar(L::kQEmpty));
         };
         while (n_s < kSBufs && n_s < n_jobs && ok) next_s();
+        // the accumulators still hold the previous item's O until the sigmoid warps have read it
+        if (act > 0) ok = ok && mbar_wait_warp(bar(L::kOEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 33);
         for (int n = 0; n < n_jobs && ok; ++n) {
           issue_pv(cp);
           cp.advance(n0, n1, kStages, kSBufs);
           if (n_s < n_jobs && ok) next_s();  // reuses the buffer the product above has just consumed
         }
         if (!ok) break;
+        mma_commit(leader, bar(L::kOFull));
         if (n0 > 0) q_par0 ^= 1u;
         if (n1 > 0) q_par1 ^= 1u;
+        ++act;
       }
     }
     }
@@ -617,8 +609,8 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     const uint64_t v_desc0 = smem_desc_sw128(smem_base + L::kVOff, 16384, 1024);
     const uint32_t v_lo = (uint32_t)v_desc0, hi = (uint32_t)(v_desc0 >> 32);
     FwdCursor c{0, 0, 0, 0u, 0, 0u, true};
-    uint32_t fix_par = 0u;       // bit st: parity of stage st's "padded V rows cleared" barrier
-    int o_cnt0 = 0, o_cnt1 = 0;  // items in which query tile 0 / 1 had work so far
+    uint32_t fix_par = 0u;  // bit st: parity of stage st's "padded V rows cleared" barrier
+    int act = 0;            // items with work so far
     bool ok = true;
     for (int k = 0; ok; ++k) {
       const int item = read_item(k);
@@ -628,13 +620,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const int n0 = it.n0, n1 = it.n1;
       const int n_jobs = n0 + n1;
       c.begin_item(n0);
+      // the accumulators still hold the previous item's O until the sigmoid warps have read it
+      if (act > 0) ok = mbar_wait_warp(bar(L::kOEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 33);
       for (int n = 0; n < n_jobs && ok; ++n) {
-        if (c.j == 0) {
-          // the accumulator of this query tile still holds its O of an earlier item until the tile's
-          // sigmoid warps have read it
-          const int uses = c.s ? o_cnt1 : o_cnt0;
-          if (uses > 0) ok = mbar_wait_warp(bar(L::kOEmpty + c.s), (uint32_t)(uses - 1) & 1u, abort_flag, kSiteBase + 33);
-        }
         if (c.fresh) {
           ok = mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
           if (c.j * kTileN + kTileN > it.Lk) {  // padded V rows are being cleared by the producer warp
@@ -657,13 +645,11 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         }
         mma_commit(leader, bar(L::kPvDone + c.buf));
         if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
-        if (c.j == (c.s ? n1 : n0) - 1) {  // the tile's last product of the item: its O is complete
-          mma_commit(leader, bar(L::kOFull + c.s));
-          if (c.s) ++o_cnt1; else ++o_cnt0;
-        }
         c.advance(n0, n1, kStages, kSBufs);
       }
       if (!ok) break;
+      mma_commit(leader, bar(L::kOFull));
+      ++act;
     }
     }
   }
@@ -679,7 +665,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c1 = p.scale * kLog2e;
     int jobs_base = 0;  // jobs of all earlier items: position of this item's first job in the S ring
-    int act = 0;        // items in which this warp's query tile had work so far
+    int act = 0;        // items with work so far
     bool ok = true;
 
     for (int k = 0; ok; ++k) {
@@ -750,15 +736,16 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           for (int c = 0; c < kDMine / 8; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
         }
       }
-      if (n_mine > 0) {
-        // this query tile's own last product (the other tile may still be working)
-        ok = mbar_wait_warp(bar(L::kOFull + s), (uint32_t)act & 1u, abort_flag, kSiteBase + 12);
+      if (it.n_max > 0) {
+        // Every sigmoid warp waits for the item's last product, also one whose tile had no work:
+        // its arrival below must not run ahead into the barrier phase of the previous item.
+        ok = mbar_wait_warp(bar(L::kOFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 12);
         if (!ok) break;
         ++act;
         tc_fence_after_sync();
         // O leaves TMEM already rounded to 16 bits, so that few registers are live across the hand-over
         uint4 w[kDMine / 32][4];
-        {
+        if (n_mine > 0) {
           const uint32_t o_addr = tmem_lane + kColO + D * s + g * kDMine;
           const bool live = row < it.Lq;
 #pragma unroll
@@ -775,11 +762,11 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
             }
           }
         }
-        // O is in registers: the next item's products may overwrite this tile's accumulator
+        // O is in registers: the next item's products may overwrite the accumulators
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kOEmpty + s));
-        if (row < it.row_lim) {
+        if (lane == 0) mbar_arrive(bar(L::kOEmpty));
+        if (n_mine > 0 && row < it.row_lim) {
 #pragma unroll
           for (int c = 0; c < kDMine / 32; ++c) {
 #pragma unroll
