@@ -69,6 +69,7 @@ struct BwdParams {
   int causal;
   int n_kvblk;  // ceil(Tk / 128)
   int n_items;  // B * H * n_kvblk
+  int group;    // (batch, head) pairs per scheduling group, >= 1 (see bwd_decode_item)
   // two counters, zero between launches: [0] items handed out beyond the first per CTA,
   // [1] CTAs that have finished (the last one clears both)
   unsigned int* ticket;
@@ -228,8 +229,15 @@ struct BwdItem {
 };
 __device__ __forceinline__ BwdItem bwd_decode_item(const BwdParams& p, int item) {
   BwdItem it;
-  const int bh = item / p.n_kvblk;
-  const int j = item - bh * p.n_kvblk;  // key tile; under a causal mask the early (heavy) ones come first
+  // Groups of `group` (batch, head) pairs: within a group every pair's key tile 0 comes first, then
+  // every pair's tile 1, ... (under a causal mask the early tiles are the heavy ones, so this is a
+  // longest-first order), while the Q / dO of one group still fit the L2.  group = 1: (batch, head)-major.
+  const int per_group = p.group * p.n_kvblk;
+  const int grp = item / per_group;
+  const int r = item - grp * per_group;
+  const int g_eff = min(p.group, p.B * p.H - grp * p.group);
+  const int j = r / g_eff;  // key tile
+  const int bh = grp * p.group + (r - j * g_eff);
   it.b = bh / p.H;
   it.h = bh - it.b * p.H;
   it.kv0 = j * kBwdTileKV;

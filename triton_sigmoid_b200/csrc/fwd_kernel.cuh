@@ -46,6 +46,7 @@ struct FwdParams {
   int causal;
   int n_qblk;   // ceil(Tq / 256)
   int n_items;  // B * H * n_qblk
+  int group;    // (batch, head) pairs per scheduling group, >= 1 (see fwd_decode_item)
   // two counters, zero between launches: [0] items handed out beyond the first per CTA,
   // [1] CTAs that have finished (the last one clears both)
   unsigned int* ticket;
@@ -228,8 +229,16 @@ struct FwdItem {
 };
 __device__ __forceinline__ FwdItem fwd_decode_item(const FwdParams& p, int item) {
   FwdItem it;
-  const int bh = item / p.n_qblk;
-  const int qi = item - bh * p.n_qblk;
+  // Items are ordered in groups of `group` (batch, head) pairs: within a group all pairs' heaviest
+  // query blocks come first, then their second heaviest, ... (a longest-first order under a causal
+  // mask, which the ticket counter turns into a balanced schedule), while the K / V of one group
+  // still fit the L2.  group = 1 is plain (batch, head)-major order.
+  const int per_group = p.group * p.n_qblk;
+  const int grp = item / per_group;
+  const int r = item - grp * per_group;
+  const int g_eff = min(p.group, p.B * p.H - grp * p.group);
+  const int qi = r / g_eff;
+  const int bh = grp * p.group + (r - qi * g_eff);
   it.b = bh / p.H;
   it.h = bh - it.b * p.H;
   const int qblk = p.causal ? (p.n_qblk - 1 - qi) : qi;  // heavy blocks of a head first

@@ -187,6 +187,21 @@ int fwd_device_info(int device, FwdDeviceInfo* out) {
   return 0;
 }
 
+// (batch, head) pairs per scheduling group of the persistent kernels.  Under a causal mask the items of
+// one head differ in weight, and handing out the heavy items of many heads first balances the CTAs; the
+// group is limited so that what its heads stream per item (`bytes_per_head`) stays within the L2.
+// Without a causal mask the plain order is kept.
+int schedule_group(bool causal, int64_t n_bh, int64_t bytes_per_head, int64_t l2_budget) {
+#ifdef SIG_SCHEDULE_GROUP
+  return SIG_SCHEDULE_GROUP;
+#endif
+  if (!causal || n_bh <= 1) return 1;
+  int64_t g = l2_budget / (bytes_per_head > 0 ? bytes_per_head : 1);
+  if (g < 1) g = 1;
+  if (g > n_bh) g = n_bh;
+  return (int)g;
+}
+
 // The pair of counters for one launch.
 unsigned int* next_ticket_pair(const FwdDeviceInfo& info, int device) {
   static std::atomic<unsigned int> next_slot[64];
@@ -221,6 +236,8 @@ int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   const int64_t n_items = (int64_t)fp.n_qblk * p->H * p->B;
   if (n_items > INT32_MAX) return fail(-2, "too many (batch, head, query block) items: %lld", (long long)n_items);
   fp.n_items = (int)n_items;
+  // K and V of one head, half of the L2 for them
+  fp.group = schedule_group(fp.causal != 0, (int64_t)p->B * p->H, (int64_t)p->Tk * D * 2 * 2, 64ll << 20);
   FwdDeviceInfo info;
   if (int rc = fwd_device_info(p->device, &info)) return rc;
   fp.ticket = next_ticket_pair(info, p->device);
@@ -267,6 +284,9 @@ int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   const int64_t n_items = (int64_t)bp.n_kvblk * p->H * p->B;
   if (n_items > INT32_MAX) return fail(-2, "too many (batch, head, key tile) items: %lld", (long long)n_items);
   bp.n_items = (int)n_items;
+  // Q, dO and the fp32 dQ accumulator of one head; a quarter of the L2 (measured: larger groups cost the
+  // reductions their locality, a few heads already balance the CTAs)
+  bp.group = schedule_group(bp.causal != 0, (int64_t)p->B * p->H, (int64_t)p->Tq * D * (2 + 2 + 4), 32ll << 20);
   FwdDeviceInfo info;
   if (int rc = fwd_device_info(p->device, &info)) return rc;
   bp.ticket = next_ticket_pair(info, p->device);
