@@ -410,12 +410,12 @@ def main():
         kb = statistics.mean(time_main_kernel("bwd", qd, kd, vd, do, **kw))
         kf = statistics.mean(time_main_kernel("fwd", qd, kd, vd, **kw))
         # DRAM bytes per (batch, token, head, d) element of one launch, from an ncu capture of a
-        # B=2 case of this workload (profiles/ncu_full_fwd_bwd_fp16_N4096_D64.md: backward 100.7 MB
-        # read + 22.7 MB written, forward 50.4 + 1.3 MB, for 2*4096*16*64 elements); DRAM traffic grows
+        # B=2 case of this workload (profiles/ncu_full_fwd_bwd_fp16_N4096_D64.md: backward 100.8 MB
+        # read + 22.9 MB written, forward 51.6 + 0.8 MB, for 2*4096*16*64 elements); DRAM traffic grows
         # in proportion to the element count, so it is scaled to this launch.
         elems = float(wl["B"]) * w["N"] * wl["H"] * w["D"]
-        traffic_bwd = 14.71 * elems if (w["D"] == 64 and not w["padded"]) else None
-        traffic_fwd = 6.16 * elems if (w["D"] == 64 and not w["padded"]) else None
+        traffic_bwd = 14.74 * elems if (w["D"] == 64 and not w["padded"]) else None
+        traffic_fwd = 6.25 * elems if (w["D"] == 64 and not w["padded"]) else None
         ach = 2.5 * F / (kb * 1e-3) / 1e12
         line["roofline"] = {"bound": "tensor", "kernel": "sigattn_bwd_kernel", "achieved": ach, "peak": pk["burst"],
                             "unit": "TFLOP/s", "frac": ach / pk["burst"], "traffic": traffic_bwd,
