@@ -10,8 +10,9 @@
  * whose work it takes over (paths relative to that repository).
  *
  * Conventions
- *  - Every pointer in SigAttnParams is a DEVICE pointer owned by the caller.  The library
- *    allocates no device memory.  All launches are asynchronous on `stream`.
+ *  - Every pointer in SigAttnParams is a DEVICE pointer owned by the caller.  The attention entry
+ *    points allocate no device memory (only the diagnostic self-test does, 4 bytes for the duration
+ *    of its call).  All launches are asynchronous on `stream`.
  *  - Strides are in ELEMENTS; the head dimension is contiguous (stride 1).  Base pointers
  *    must be 16-byte aligned and every stride times the element size a multiple of 16 bytes.
  *  - The tensor-core kernels are persistent (one CTA per SM draws work items from a counter).  Each
