@@ -42,7 +42,18 @@ extern "C" {
 enum SigAttnDtype { SIGATTN_FP16 = 0, SIGATTN_BF16 = 1, SIGATTN_FP32 = 2 };
 
 enum SigAttnFlags {
-  SIGATTN_CAUSAL = 1u << 0, /* key j visible to query i only if j <= i */
+  SIGATTN_CAUSAL = 1u << 0,   /* key j visible to query i only if j <= i */
+  /* Accurate sigmoid in the tensor-core kernels: exponential and reciprocal both on the special-function
+   * unit (relative error ~2^-22) instead of the default one-exponential form with a polynomial
+   * reciprocal or a short series.  Counterpart of the reference's TRITON_SIGMOID_ACCURATE switch
+   * (src/triton_sigmoid/kernel_utils.py:190-193, 236-237); slower.  Ignored for fp32 (always exact). */
+  SIGATTN_ACCURATE = 1u << 1,
+  /* Backward only: use the pair of streaming kernels (dK/dV with the keys stationary, then dQ with the
+   * queries stationary; 7 GEMMs per tile pair like the reference's split, sigmoid_triton_dense.py:162-467)
+   * instead of the default fused kernel (5 GEMMs, dQ accumulated with fp32 reductions into `workspace`).
+   * The split needs no workspace, uses no atomics and is run-to-run deterministic; the fused kernel was
+   * measured faster and is therefore the default. */
+  SIGATTN_BWD_SPLIT = 1u << 2,
 };
 
 enum SigAttnQuery {

@@ -13,9 +13,28 @@ def _qkv(B=2, T=32, H=2, D=64, dtype=torch.float16):
 
 
 def test_exports_match_reference_package():
-    """The reference's three names, plus the packed variable-length entry point it does not have."""
+    """The reference's three names, plus what it does not have: the packed variable-length entry point and
+    the two run-time helpers (accurate-sigmoid switch, device health word)."""
     assert set(m.__all__) == {"sigmoid_attention", "sigmoid_attention_padded", "sigmoid_attention_ref",
-                              "sigmoid_attention_varlen"}
+                              "sigmoid_attention_varlen", "accurate_sigmoid", "device_status"}
+
+
+def test_accurate_switch_follows_the_reference_variable(monkeypatch):
+    """TRITON_SIGMOID_ACCURATE takes the reference's values (kernel_utils.py:190-193 there), read per call;
+    the context manager overrides it."""
+    monkeypatch.delenv("TRITON_SIGMOID_ACCURATE", raising=False)
+    assert not ops._accurate()
+    for v in ("1", "true", "YES", "On"):
+        monkeypatch.setenv("TRITON_SIGMOID_ACCURATE", v)
+        assert ops._accurate()
+    monkeypatch.setenv("TRITON_SIGMOID_ACCURATE", "0")
+    assert not ops._accurate()
+    with m.accurate_sigmoid(True):
+        assert ops._accurate() and ops._flags(True) == 3
+        with m.accurate_sigmoid(False):
+            assert not ops._accurate() and ops._flags(False) == 0
+        assert ops._accurate()
+    assert not ops._accurate()
 
 
 def test_varlen_argument_errors():

@@ -46,6 +46,20 @@ def test_raw_forward_and_backward_calls():
     assert (o.float().cpu() - ref_o).abs().max().item() <= 2e-3
     for g, r in zip((dq, dk, dv), ref):
         assert ((g.float().cpu() - r).norm() / r.norm()).item() <= 1e-2
+    # the split backward (streaming kernels): no workspace, against the oracle, and run-to-run deterministic
+    p.workspace, p.workspace_bytes = None, 0
+    p.flags |= _cabi.SIGATTN_BWD_SPLIT
+    runs = []
+    for _ in range(2):
+        outs = [torch.full_like(q, float("nan")) for _ in range(3)]
+        p.dq, p.dk, p.dv = [t.data_ptr() for t in outs]
+        assert lib.sigattn_bwd(ctypes.byref(p)) == 0, lib.sigattn_last_error()
+        runs.append(outs)
+    assert lib.sigattn_device_status(0) == 0
+    for g, r in zip(runs[0], ref):
+        assert ((g.float().cpu() - r).norm() / r.norm()).item() <= 1e-2
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)
 
 
 def test_workspace_too_small_is_reported():

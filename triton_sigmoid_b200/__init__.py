@@ -7,11 +7,17 @@ Both functions run hand-written CUDA kernels through a C-ABI shared library
 ``sigmoid_attention_varlen`` is the same computation on packed variable-length sequences (not in
 the reference).  ``sigmoid_attention_ref`` is the plain PyTorch formula, exported because the reference
 package exports one too; it is not used by the two functions above.
+
+Run-time switches: ``TRITON_SIGMOID_ACCURATE=1`` (the reference's variable, read at every call) or the
+``accurate_sigmoid()`` context manager select the accurate sigmoid; ``SIGATTN_B200_DEBUG=1`` makes every
+call synchronise and raise if a kernel gave up on one of its bounded waits; ``device_status()`` reads
+and clears that health word on demand.
 """
 
 __version__ = "0.1.0"
 
-from .ops import sigmoid_attention, sigmoid_attention_padded, sigmoid_attention_varlen
+from .ops import (accurate_sigmoid, device_status, sigmoid_attention, sigmoid_attention_padded,
+                  sigmoid_attention_varlen)
 from .reference_math import sigmoid_attention_ref
 
 __all__ = [
@@ -19,4 +25,6 @@ __all__ = [
     "sigmoid_attention_padded",
     "sigmoid_attention_varlen",
     "sigmoid_attention_ref",
+    "accurate_sigmoid",
+    "device_status",
 ]

@@ -16,6 +16,8 @@ SIGATTN_FP16 = 0
 SIGATTN_BF16 = 1
 SIGATTN_FP32 = 2
 SIGATTN_CAUSAL = 1
+SIGATTN_ACCURATE = 2
+SIGATTN_BWD_SPLIT = 4
 SIGATTN_STATIC_SCRATCH_ELEMS = 8 * 1024 * 1024
 
 Q_ABI_VERSION, Q_SM_ARCH, Q_MAX_HEAD_DIM, Q_PARAMS_SIZE = 0, 1, 2, 3

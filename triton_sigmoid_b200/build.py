@@ -42,13 +42,13 @@ def find_nvcc() -> str:
     raise RuntimeError("nvcc not found: set NVCC or put it on PATH")
 
 
-def build(force: bool = False, verbose: bool = False, out: str = None, extra_flags=()) -> str:
-    """Compile the library.  `out` / `extra_flags` build a variant elsewhere (experiments)."""
-    target = out or LIB_PATH
-    if out is None and not force and not needs_build():
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the library (skipped when it is newer than its sources, unless `force`)."""
+    target = LIB_PATH
+    if not force and not needs_build():
         return LIB_PATH
     os.makedirs(os.path.dirname(target), exist_ok=True)
-    cmd = [find_nvcc(), *NVCC_FLAGS, *extra_flags]
+    cmd = [find_nvcc(), *NVCC_FLAGS]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", target, os.path.join(CSRC, "sigattn_api.cu")]

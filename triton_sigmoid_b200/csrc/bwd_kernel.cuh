@@ -22,13 +22,12 @@
 //                                D = 128: the transposed product dQ^T = K^T dS^T is computed
 //                                  instead; the head dimension lies on the lanes and one
 //                                  red.global.add.f32 per query covers a full 128-byte line;
-//                                D = 64: M = 64 would idle half of the tensor core and half of
-//                                  the lanes, and staging rows in shared memory for bulk
-//                                  the lanes, so each warp takes full 128-byte half rows of every
-//                                  second query row, regrouped through a private shared-memory
-//                                  patch so that eight lanes cover a line, and adds them with
-//                                  red.global.add.v4.f32 (the reduction traffic, not the math,
-//                                  is what bounds this case).
+//                                D = 64: the transposed product would have M = 64 and idle half of
+//                                  the tensor core and half of the lanes, so dQ is kept as it is and
+//                                  each warp takes full 128-byte half rows of every second query row,
+//                                  regrouped through a private shared-memory patch so that eight
+//                                  lanes cover a line, and adds them with red.global.add.v4.f32
+//                                  (the reduction traffic, not the math, is what bounds this case).
 //
 // Warp roles (20 warps):
 //   warps 0-15  compute: warp w owns TMEM lanes (key rows) 32 (w & 3) .. +31 and the query
@@ -132,7 +131,7 @@ struct BwdSmem {
 // Phase A of one tile for one thread: 32 scores of its key row -> probabilities (kept in pv[]
 // for phase B) and their 16-bit packing written over the first 16 of the 32 columns read.
 // q0 = query index of the first column; valid queries for this key row are [q_lo, q_hi).
-template <bool kBF16, bool kMask>
+template <bool kBF16, bool kMask, bool kAccurate>
 __device__ __forceinline__ void bwd_phase_a(uint32_t s_addr, float c1, float c0, int q0, int q_lo, int q_hi,
                                             float (&pv)[32]) {
   uint32_t r[32];
@@ -140,11 +139,26 @@ __device__ __forceinline__ void bwd_phase_a(uint32_t s_addr, float c1, float c0,
   uint32_t pk[16];
   float2 t[16];
   // unmasked tiles work on logits shifted up by kDeepShift (see sigmoid2_from_shifted_log2_deep)
-  const float c0s = kMask ? c0 : c0 + kDeepShift;
+  const float c0s = (kMask || kAccurate) ? c0 : c0 + kDeepShift;
 #pragma unroll
   for (int i = 0; i < 16; ++i)
     t[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), make_float2(c1, c1),
                       make_float2(c0s, c0s));
+  if constexpr (kAccurate) {
+    // exponential and reciprocal both on the special-function unit (see sigmoid2_accurate_from_log2)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float2 pe = sigmoid2_accurate_from_log2(t[i]);
+      if constexpr (kMask) {
+        const int q = q0 + 2 * i;
+        pe.x = (q >= q_lo && q < q_hi) ? pe.x : 0.0f;
+        pe.y = (q + 1 >= q_lo && q + 1 < q_hi) ? pe.y : 0.0f;
+      }
+      pv[2 * i] = pe.x;
+      pv[2 * i + 1] = pe.y;
+      pk[i] = pack2<kBF16>(pe.x, pe.y);
+    }
+  } else
   // all logits far below zero (the usual case under the default bias): short series, no compare / select per element
   if (!kMask && warp_all_negative(t)) {
 #pragma unroll
@@ -266,7 +280,7 @@ __device__ __forceinline__ BwdItem bwd_decode_item(const BwdParams& p, int item)
   return it;
 }
 
-template <int D, bool kBF16>
+template <int D, bool kBF16, bool kAccurate>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                    const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap do_map,
@@ -741,8 +755,8 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         const uint32_t s_addr = s_addr0 + 128u * (uint32_t)sbuf(gt);
         if (!ok) break;
         tc_fence_after_sync();
-        if (need_mask) bwd_phase_a<kBF16, true>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
-        else           bwd_phase_a<kBF16, false>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
+        if (need_mask) bwd_phase_a<kBF16, true, kAccurate>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
+        else           bwd_phase_a<kBF16, false, kAccurate>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();

@@ -8,17 +8,26 @@
 // (src/triton_sigmoid/sigmoid_triton_padded.py:24-171).
 //
 // Structure (sm_100a, 20 warps):
-//   warps 0-7    sigmoid groups of query tile 0 (rows [q0, q0+128)): warps 0-3 take key columns
-//                [0,64) of every score tile, warps 4-7 columns [64,128); one thread per row
-//   warps 8-15   the same for query tile 1 (rows [q0+128, q0+256))
+//   warps 0-15   sigmoid warps.  A JOB is one query tile (128 rows) times one key tile (128 columns);
+//                one thread per row, 32-column chunks, P written over the start of the chunk's columns.
+//                D = 128: all sixteen warps work on the same job (warp w: TMEM lanes 32 (w & 3) ..,
+//                key columns 32 (w >> 2) ..).  With eight warps per job and two jobs in the sigmoid
+//                stage at a time, a score buffer stays occupied for about three job times, and the two
+//                buffers TMEM has room for at D = 128 starve the sigmoid warps (measured: 44 % of their
+//                time waiting for scores); with sixteen warps per job it is occupied for about two.
+//                D = 64: warps 0-7 take the jobs of query tile 0, warps 8-15 those of tile 1 (warp w:
+//                lanes 32 (w & 3) .., columns 64 ((w >> 2) & 1) .., two chunks per job, the second
+//                loaded while the first is computed); three buffers are enough for that, and the
+//                per-job costs (barrier round trip, exposed TMEM load) are paid once per 64 columns
+//                (measured faster at D = 64 than sixteen warps per job: 728 against 647 TFLOP/s).
 //   warp  16     item scheduler + TMA producer: Q tiles per item, K_j / V_j through a ring of smem stages
 //   warp  17     tcgen05 issuer 1: S = Q_s K_j^T (smem x smem -> TMEM fp32); owns the TMEM allocation
 //   warp  18     tcgen05 issuer 2: O_s += P V_j (TMEM x smem -> TMEM fp32)
 // There is no row normaliser in sigmoid attention, so O simply accumulates in TMEM over the
 // whole key loop of an item.  The (query tile, key tile) jobs are processed in a fixed order through a
 // small ring of S buffers in TMEM (3 when D = 64, 2 when D = 128): the issuer computes the
-// scores of a later job while the sigmoid groups turn earlier ones into 16-bit P in place
-// (each group writes P over the start of the columns it has just read) and signal the issuer.
+// scores of a later job while the sigmoid warps turn an earlier one into 16-bit P in place
+// (each warp writes P over the start of the columns it has just read) and signal the issuer.
 //
 // Masking: key tiles beyond the causal diagonal or the valid key length are skipped
 // entirely; tiles that straddle either boundary apply an element predicate.
@@ -52,24 +61,15 @@ struct FwdParams {
   unsigned int* ticket;
 };
 
-#ifndef SIG_FWD_CHUNK
-#define SIG_FWD_CHUNK 32  // score columns per TMEM load of a sigmoid thread (32 measured faster than 16)
-#endif
-#ifndef SIG_FWD_HALVES
-#define SIG_FWD_HALVES 2  // sigmoid warps per (query tile, lane quarter): 2 = each takes 64 of the 128 key columns
-#endif
-constexpr int kFwdHalves = SIG_FWD_HALVES;
-constexpr int kFwdSigmoidWarps = 8 * kFwdHalves;
+constexpr int kFwdSigmoidWarps = 16;
 constexpr int kFwdProducerWarp = kFwdSigmoidWarps;
 constexpr int kFwdIssuerWarp = kFwdSigmoidWarps + 1;   // S = Q K^T, owns the TMEM allocation
 constexpr int kFwdIssuerWarp2 = kFwdSigmoidWarps + 2;  // O += P V
 constexpr int kFwdThreads = (kFwdSigmoidWarps + 4) * 32;  // the role warps form a register-allocation group of four
 constexpr int kFwdLaunchRegs = 96;  // what 640 threads per CTA get each: 65536 / 640, rounded down to a multiple of 8
-static_assert(kFwdThreads == 640, "the register re-allocation below is worked out for 20 warps (SIG_FWD_HALVES = 2)");
 // Registers per thread after the re-allocation: the role warps (a group of four) and the sigmoid warps.
-// D = 64: the role warps fit in 32; D = 128: the single issuing warp carries two job cursors.
 template <int D> struct FwdRegs {
-  static constexpr int kRole = (D == 64) ? 32 : 64;
+  static constexpr int kRole = (D == 64) ? 32 : 40;
   static constexpr int kSigmoid = (D == 64) ? 112 : 104;
   static_assert(kFwdSigmoidWarps * 32 * kSigmoid + 128 * kRole <= kFwdThreads * kFwdLaunchRegs,
                 "the re-allocation may not ask for more registers than the CTA holds");
@@ -136,58 +136,64 @@ struct FwdCursor {
   }
 };
 
-// Turns 64 score columns of one TMEM lane (this thread's query row) into 16-bit probabilities,
-// written back over the first 32 of those columns.  col0 = key index of the first column,
-// lim = largest visible key index of this row (used only when kMask).
-template <bool kBF16, bool kScoreMod, bool kMask>
-__device__ __forceinline__ void fwd_sigmoid_half_tile(uint32_t s_addr, float c1, float c0, int col0, int lim,
-                                                      const float* sm_row, int Tk) {
-  // two register buffers: the load of the next chunk is in flight while one is computed
-  constexpr int kCh = SIG_FWD_CHUNK;  // score columns per chunk
-  constexpr int kNCh = 64 / kCh;
-  uint32_t rbuf[2][kCh];
-  tmem_ld(s_addr, rbuf[0]);
+// 32 score columns of one TMEM lane (this thread's query row), already in registers -> logits in the
+// base-2 domain, t = (scale * s + bias (+ score_mod[key])) * log2(e).  Chunks that need no element
+// predicate work on logits shifted up by kDeepShift (see sigmoid2_from_shifted_log2_deep).
+// col0 = key index of the first column.
+template <bool kScoreMod, bool kMask, bool kAccurate>
+__device__ __forceinline__ void fwd_chunk_logits(const uint32_t (&r)[32], float2 (&t)[16], float c1, float c0, int col0,
+                                                 const float* sm_row, int Tk) {
+  constexpr int kCh = 32;
+  constexpr bool kShift = !kMask && !kAccurate;
+  const float c0s = kShift ? c0 + kDeepShift : c0;
 #pragma unroll
-  for (int c = 0; c < kNCh; ++c) {
-    uint32_t(&r)[kCh] = rbuf[c & 1];
-    tmem_ld_wait_for(r);
-    if (c + 1 < kNCh) tmem_ld(s_addr + (c + 1) * kCh, rbuf[(c + 1) & 1]);
-    uint32_t pk[kCh / 2];
-    float2 t[kCh / 2];
-    // unmasked tiles work on logits shifted up by kDeepShift (see sigmoid2_from_shifted_log2_deep)
-    const float c0s = kMask ? c0 : c0 + kDeepShift;
+  for (int i = 0; i < kCh / 2; ++i) {
+    t[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), make_float2(c1, c1),
+                      make_float2(c0s, c0s));
+  }
+  if constexpr (kScoreMod) {
+    // per-key additive bias: the same value for every lane (row), read through the read-only path
+    if (col0 + kCh <= Tk && (reinterpret_cast<uintptr_t>(sm_row + col0) & 15u) == 0) {
 #pragma unroll
-    for (int i = 0; i < kCh / 2; ++i) {
-      t[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), make_float2(c1, c1),
-                        make_float2(c0s, c0s));
-    }
-    if constexpr (kScoreMod) {
-      // per-key additive bias: the same value for every lane (row), read through the read-only path
-      const int cbase = col0 + c * kCh;
-      if (cbase + kCh <= Tk && (reinterpret_cast<uintptr_t>(sm_row + cbase) & 15u) == 0) {
+      for (int i = 0; i < kCh / 4; ++i) {
+        const float4 m = __ldg(reinterpret_cast<const float4*>(sm_row + col0) + i);
+        t[2 * i] = __ffma2_rn(make_float2(m.x, m.y), make_float2(kLog2e, kLog2e), t[2 * i]);
+        t[2 * i + 1] = __ffma2_rn(make_float2(m.z, m.w), make_float2(kLog2e, kLog2e), t[2 * i + 1]);
+      }
+    } else {
 #pragma unroll
-        for (int i = 0; i < kCh / 4; ++i) {
-          const float4 m = __ldg(reinterpret_cast<const float4*>(sm_row + cbase) + i);
-          t[2 * i] = __ffma2_rn(make_float2(m.x, m.y), make_float2(kLog2e, kLog2e), t[2 * i]);
-          t[2 * i + 1] = __ffma2_rn(make_float2(m.z, m.w), make_float2(kLog2e, kLog2e), t[2 * i + 1]);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < kCh / 2; ++i) {
-          const int col = cbase + 2 * i;
-          t[i].x = fmaf(col < Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t[i].x);
-          t[i].y = fmaf(col + 1 < Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t[i].y);
-        }
+      for (int i = 0; i < kCh / 2; ++i) {
+        const int col = col0 + 2 * i;
+        t[i].x = fmaf(col < Tk ? __ldg(sm_row + col) : 0.0f, kLog2e, t[i].x);
+        t[i].y = fmaf(col + 1 < Tk ? __ldg(sm_row + col + 1) : 0.0f, kLog2e, t[i].y);
       }
     }
+  }
+}
+
+// Logits of fwd_chunk_logits -> 16-bit probabilities, written over the first 16 of the chunk's 32 TMEM
+// columns at s_addr.  lim = largest visible key index of this row (used only when kMask).
+template <bool kBF16, bool kMask, bool kAccurate>
+__device__ __forceinline__ void fwd_chunk_probs(uint32_t s_addr, float2 (&t)[16], int col0, int lim) {
+  constexpr int kCh = 32;
+  uint32_t pk[kCh / 2];
+  if constexpr (kAccurate) {
+#pragma unroll
+    for (int i = 0; i < kCh / 2; ++i) {
+      float2 pr = sigmoid2_accurate_from_log2(t[i]);
+      if constexpr (kMask) {
+        const int col = col0 + 2 * i;
+        pr.x = (col <= lim) ? pr.x : 0.0f;
+        pr.y = (col + 1 <= lim) ? pr.y : 0.0f;
+      }
+      pk[i] = pack2<kBF16>(pr.x, pr.y);
+    }
+  } else {
     // Under the default bias every logit of a chunk is far below zero: the short series applies
     // and the sign handling (one compare and one select per element) is skipped for the whole warp.
     if (!kMask && warp_all_negative(t)) {
 #pragma unroll
-      for (int i = 0; i < kCh / 2; ++i) {
-        const float2 pr = sigmoid2_from_shifted_log2_deep<kBF16>(t[i]);
-        pk[i] = pack2<kBF16>(pr.x, pr.y);
-      }
+      for (int i = 0; i < kCh / 2; ++i) pk[i] = sigmoid2_deep_packed<kBF16>(t[i], (i & 7) == 7);
     } else {
       bool all_neg = false;
       if constexpr (!kMask) {
@@ -201,20 +207,30 @@ __device__ __forceinline__ void fwd_sigmoid_half_tile(uint32_t s_addr, float c1,
           const float2 pr = sigmoid2_from_log2_neg<kBF16>(t[i]);
           pk[i] = pack2<kBF16>(pr.x, pr.y);
         }
-      } else
+      } else {
 #pragma unroll
-      for (int i = 0; i < kCh / 2; ++i) {
-        float2 pr = sigmoid2_from_log2<kBF16>(t[i]);
-        if constexpr (kMask) {
-          const int col = col0 + c * kCh + 2 * i;
-          pr.x = (col <= lim) ? pr.x : 0.0f;
-          pr.y = (col + 1 <= lim) ? pr.y : 0.0f;
+        for (int i = 0; i < kCh / 2; ++i) {
+          float2 pr = sigmoid2_from_log2<kBF16>(t[i]);
+          if constexpr (kMask) {
+            const int col = col0 + 2 * i;
+            pr.x = (col <= lim) ? pr.x : 0.0f;
+            pr.y = (col + 1 <= lim) ? pr.y : 0.0f;
+          }
+          pk[i] = pack2<kBF16>(pr.x, pr.y);
         }
-        pk[i] = pack2<kBF16>(pr.x, pr.y);
       }
     }
-    tmem_st(s_addr + c * (kCh / 2), pk);
   }
+  tmem_st(s_addr, pk);
+}
+
+// Both steps for a chunk whose scores are in registers.
+template <bool kBF16, bool kScoreMod, bool kMask, bool kAccurate>
+__device__ __forceinline__ void fwd_sigmoid_chunk(uint32_t s_addr, const uint32_t (&r)[32], float c1, float c0, int col0,
+                                                  int lim, const float* sm_row, int Tk) {
+  float2 t[16];
+  fwd_chunk_logits<kScoreMod, kMask, kAccurate>(r, t, c1, c0, col0, sm_row, Tk);
+  fwd_chunk_probs<kBF16, kMask, kAccurate>(s_addr, t, col0, lim);
 }
 
 // One work item, decoded the same way by every warp role.
@@ -274,7 +290,7 @@ __device__ __forceinline__ FwdItem fwd_decode_item(const FwdParams& p, int item)
   return it;
 }
 
-template <int D, bool kBF16, bool kScoreMod>
+template <int D, bool kBF16, bool kScoreMod, bool kAccurate>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                    const __grid_constant__ CUtensorMap v_map, const FwdParams p) {
@@ -288,7 +304,8 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   constexpr int kSiteBase = 0x10000;
   // D = 64: scores and P V are issued by two warps (the issue stream bounds the kernel); D = 128:
   // one warp issues both, in order - with only two S buffers the extra barrier hop costs more
-  constexpr bool kSplitIssue = (D == 64);
+  constexpr bool kSplitIssue = true;
+  constexpr int kJobWarps = (D == 64) ? 8 : 16;  // sigmoid warps per job (see the file header)
   // warps that read the published item index: the sigmoid warps and the issuing warp(s)
   constexpr int kItemReaders = kFwdSigmoidWarps + (kSplitIssue ? 2 : 1);
   static_assert(kColO + 2 * D <= kTmemCols, "TMEM budget");
@@ -321,7 +338,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     }
     for (int i = 0; i < kSBufs; ++i) {
       mbar_init(bar(L::kSFull + i), 1);
-      mbar_init(bar(L::kPFull + i), 4 * kFwdHalves);  // one arrival per sigmoid warp of the query tile
+      mbar_init(bar(L::kPFull + i), kJobWarps);  // one arrival per sigmoid warp of the job
       mbar_init(bar(L::kPvDone + i), 1);
     }
     mbar_init(bar(L::kOFull), 1);
@@ -566,8 +583,8 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         const uint32_t acc0 = c.j > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < kTileN / 16; ++kk) {
-          // P of key columns [64g, 64g+64) sits, 16-bit packed, in buffer columns 64g + [0,32)
-          mma_ts(leader, dst, pa + 64 * (kk >> 2) + 8 * (kk & 3), make_desc(va + kk * (2048 >> 4), v_hi), idesc_pv,
+          // P of key columns [32g, 32g+32) sits, 16-bit packed, in buffer columns 32g + [0,16)
+          mma_ts(leader, dst, pa + 32 * (kk >> 1) + 8 * (kk & 1), make_desc(va + kk * (2048 >> 4), v_hi), idesc_pv,
                  kk > 0 ? 1u : acc0);
         }
         if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
@@ -648,8 +665,8 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         const uint32_t acc0 = c.j > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < kTileN / 16; ++kk) {
-          // P of key columns [64g, 64g+64) sits, 16-bit packed, in buffer columns 64g + [0,32)
-          mma_ts(leader, dst, pa + 64 * (kk >> 2) + 8 * (kk & 3), make_desc(va + kk * (2048 >> 4), hi), idesc_pv,
+          // P of key columns [32g, 32g+32) sits, 16-bit packed, in buffer columns 32g + [0,16)
+          mma_ts(leader, dst, pa + 32 * (kk >> 1) + 8 * (kk & 1), make_desc(va + kk * (2048 >> 4), hi), idesc_pv,
                  kk > 0 ? 1u : acc0);
         }
         mma_commit(leader, bar(L::kPvDone + c.buf));
@@ -664,110 +681,164 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   }
   }  // role warps
   else {
-    // ============================================================ sigmoid groups + epilogue
+    // ============================================================ sigmoid warps + epilogue
     setmaxnreg_inc<FwdRegs<D>::kSigmoid>();
-    const int s = warp / (4 * kFwdHalves);                // query tile
-    const int g = kFwdHalves == 2 ? (warp >> 2) & 1 : 0;  // which half of the key columns (when split)
-    constexpr int kColsMine = 128 / kFwdHalves;           // key columns per thread and job
-    constexpr int kDMine = D / kFwdHalves;                // output columns per thread
-    const int lane_row = (warp & 3) * 32 + lane;          // TMEM lane == row within the tile
+    const int cq = warp >> 2;                         // quarter of a job's key columns (16 warps per job) / of the head dimension in the epilogue
+    const int lane_row = (warp & 3) * 32 + lane;      // TMEM lane == row within a query tile
     const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c1 = p.scale * kLog2e;
-    int jobs_base = 0;  // jobs of all earlier items: position of this item's first job in the S ring
-    int act = 0;        // items with work so far
+    int buf = 0;          // 16 warps per job: S buffer of the next job
+    uint32_t bph = 0u;    //                   and the parity of that buffer's barriers
+    int jobs_base = 0;    // 8 warps per job: jobs of all earlier items, position of this item's first job in the S ring
+    int act = 0;          // items with work so far
     bool ok = true;
 
     for (int k = 0; ok; ++k) {
       // The ring slot keeps the item until this warp releases it at the end of the item, so what
       // only the epilogue needs is decoded again there instead of being held in registers.
-      const int slot = k & 1;
-      ok = mbar_wait_warp(bar(L::kItemFull + slot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30);
+      const int islot = k & 1;
+      ok = mbar_wait_warp(bar(L::kItemFull + islot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30);
       if (!ok) break;
-      const int item = item_ring[slot];
+      const int item = item_ring[islot];
       if (item < 0) break;
-      int n0, n1, n_mine, lim, mask_from, sm_lim = 0;
+      int n0, n1, q0, Lk;
       float c0;
       const float* sm_row = nullptr;
+      int sm_lim = 0;
       {
         const FwdItem it = fwd_decode_item(p, item);
         n0 = it.n0;
         n1 = it.n1;
-        n_mine = s == 0 ? n0 : n1;
-        const int row = it.q0 + 128 * s + lane_row;  // query index
-        // largest visible key index for this row
-        lim = it.Lk - 1;
-        if (p.causal) lim = min(lim, row);
-        // a 64-column block needs the element predicate when it reaches beyond this key index
-        mask_from = it.Lk;
-        if (p.causal) mask_from = min(mask_from, it.q0 + 128 * s + 1);
+        q0 = it.q0;
+        Lk = it.Lk;
         c0 = (p.bias ? p.bias[it.b] : p.bias_scalar) * kLog2e;
         if constexpr (kScoreMod) {
           sm_row = p.score_mod + (p.cu_k ? (int64_t)it.tk0 : (int64_t)it.b * p.Tk);
           sm_lim = it.key_lim;
         }
       }
-
-      for (int j = 0; j < n_mine; ++j) {
-        // jobs are ordered by key tile, query tile 0 before 1: (0,0) (1,0) (0,1) (1,1) ...
-        const int n = jobs_base + (s == 0 ? j + min(j, n1) : j + min(j + 1, n0));
-        const int buf = n % kSBufs;
-        ok = mbar_wait_warp(bar(L::kSFull + buf), (uint32_t)(n / kSBufs) & 1u, abort_flag, kSiteBase + 10 + s);
-        if (!ok) break;
-        tc_fence_after_sync();
+      // per query tile: largest visible key index of this thread's row, and the first key index at which a
+      // chunk needs the element predicate (it reaches beyond the keys every row of the tile sees)
+      int lim[2], mask_from[2];
 #pragma unroll
-        for (int hh = 0; hh < kColsMine / 64; ++hh) {
-          const uint32_t s_addr = tmem_lane + kColS + 128 * buf + 64 * (g + hh);
-          const int col0 = j * kTileN + 64 * (g + hh);
-          // the predicate code exists only in the instantiation used by boundary tiles
-          if (col0 + 64 > mask_from)
-            fwd_sigmoid_half_tile<kBF16, kScoreMod, true>(s_addr, c1, c0, col0, lim, sm_row, sm_lim);
-          else
-            fwd_sigmoid_half_tile<kBF16, kScoreMod, false>(s_addr, c1, c0, col0, lim, sm_row, sm_lim);
+      for (int s = 0; s < 2; ++s) {
+        lim[s] = Lk - 1;
+        mask_from[s] = Lk;
+        if (p.causal) {
+          lim[s] = min(lim[s], q0 + 128 * s + lane_row);
+          mask_from[s] = min(mask_from[s], q0 + 128 * s + 1);
         }
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kPFull + buf));  // 256 arrivals on one barrier would serialise
+      }
+      const int n_max = max(n0, n1);
+
+      if constexpr (kJobWarps == 16) {
+        // every warp works on every job, in the fixed order (0,0) (1,0) (0,1) (1,1) ... restricted to j < n_s
+        // (loading the next job's scores under this job's arithmetic was measured much slower: the second
+        // register buffer makes the compiler spill inside the loop)
+        for (int j = 0; j < n_max && ok; ++j) {
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            if (j < (s == 0 ? n0 : n1)) {
+              ok = ok && mbar_wait_warp(bar(L::kSFull + buf), bph, abort_flag, kSiteBase + 10 + s);
+              if (ok) {
+                tc_fence_after_sync();
+                const uint32_t s_addr = tmem_lane + kColS + 128u * (uint32_t)buf + 32u * (uint32_t)cq;
+                const int col0 = j * kTileN + 32 * cq;
+                uint32_t r[32];
+                tmem_ld32_sync(s_addr, r);
+                // the predicate code exists only in the instantiation used by boundary chunks
+                if (col0 + 32 > mask_from[s])
+                  fwd_sigmoid_chunk<kBF16, kScoreMod, true, kAccurate>(s_addr, r, c1, c0, col0, lim[s], sm_row, sm_lim);
+                else
+                  fwd_sigmoid_chunk<kBF16, kScoreMod, false, kAccurate>(s_addr, r, c1, c0, col0, lim[s], sm_row, sm_lim);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(L::kPFull + buf));  // one arrival per warp: 512 on one barrier would serialise
+                if (++buf == kSBufs) { buf = 0; bph ^= 1u; }
+              }
+            }
+          }
+        }
+      } else {
+        // warps 0-7: jobs of query tile 0, warps 8-15: tile 1; each warp 64 key columns of its jobs
+        const int s = warp >> 3;
+        const int g = (warp >> 2) & 1;
+        const int n_mine = s == 0 ? n0 : n1;
+        for (int j = 0; j < n_mine; ++j) {
+          // jobs are ordered by key tile, query tile 0 before 1: (0,0) (1,0) (0,1) (1,1) ...
+          const int n = jobs_base + (s == 0 ? j + min(j, n1) : j + min(j + 1, n0));
+          const int jb = n % kSBufs;
+          ok = mbar_wait_warp(bar(L::kSFull + jb), (uint32_t)(n / kSBufs) & 1u, abort_flag, kSiteBase + 10 + s);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t s_addr = tmem_lane + kColS + 128u * (uint32_t)jb + 64u * (uint32_t)g;
+          const int col0 = j * kTileN + 64 * g;
+          // two register buffers: the load of the second chunk is in flight while the first is computed
+          uint32_t rbuf[2][32];
+          tmem_ld(s_addr, rbuf[0]);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t(&r)[32] = rbuf[c];
+            tmem_ld_wait_for(r);
+            if (c == 0) tmem_ld(s_addr + 32, rbuf[1]);
+            if (col0 + 32 * c + 32 > mask_from[s])
+              fwd_sigmoid_chunk<kBF16, kScoreMod, true, kAccurate>(s_addr + 32 * c, r, c1, c0, col0 + 32 * c, lim[s], sm_row, sm_lim);
+            else
+              fwd_sigmoid_chunk<kBF16, kScoreMod, false, kAccurate>(s_addr + 32 * c, r, c1, c0, col0 + 32 * c, lim[s], sm_row, sm_lim);
+          }
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(L::kPFull + jb));  // one arrival per warp: 256 on one barrier would serialise
+        }
+        if (!ok) break;
+        jobs_base += n0 + n1;
       }
       if (!ok) break;
-      jobs_base += n0 + n1;
 
       // ---------------------------------------------------------- epilogue of the item
-      const FwdItem it = fwd_decode_item(p, item_ring[slot]);
-      const int row = it.q0 + 128 * s + lane_row;
-      // this thread's output columns (16-bit)
-      uint8_t* o_row = reinterpret_cast<uint8_t*>(p.o) +
-                       2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)(it.tq0 + row) * p.o_st) + g * D;
-      if (n_mine == 0) {
-        // this tile is entirely padding (or beyond Tq): zero rows
-        if (row < it.row_lim) {
-#pragma unroll
-          for (int c = 0; c < kDMine / 8; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
-        }
-      }
-      if (it.n_max > 0) {
-        // Every sigmoid warp waits for the item's last product, also one whose tile had no work:
-        // its arrival below must not run ahead into the barrier phase of the previous item.
+      // Every warp takes its lane quarter and a quarter of the head dimension of BOTH query tiles.
+      const FwdItem it = fwd_decode_item(p, item_ring[islot]);
+      constexpr int kDMine = D / 4;  // output columns per thread and tile
+      uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) +
+                        2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)(it.tq0 + it.q0) * p.o_st) +
+                        2 * cq * kDMine;
+      uint4 w[2][kDMine / 8];
+      if (n_max > 0) {
         ok = mbar_wait_warp(bar(L::kOFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 12);
         if (!ok) break;
         ++act;
         tc_fence_after_sync();
         // O leaves TMEM already rounded to 16 bits, so that few registers are live across the hand-over
-        uint4 w[kDMine / 32][4];
-        if (n_mine > 0) {
-          const uint32_t o_addr = tmem_lane + kColO + D * s + g * kDMine;
-          const bool live = row < it.Lq;
 #pragma unroll
-          for (int c = 0; c < kDMine / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32_sync(o_addr + c * 32, r);
+        for (int s = 0; s < 2; ++s) {
+          if ((s == 0 ? n0 : n1) > 0) {
+            const uint32_t o_addr = tmem_lane + kColO + D * s + cq * kDMine;
+            const bool live = it.q0 + 128 * s + lane_row < it.Lq;
+            if constexpr (kDMine == 32) {
+              uint32_t r[32];
+              tmem_ld32_sync(o_addr, r);
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              w[c][q4].x = pack2<kBF16>(__uint_as_float(r[8 * q4 + 0]), __uint_as_float(r[8 * q4 + 1]));
-              w[c][q4].y = pack2<kBF16>(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3]));
-              w[c][q4].z = pack2<kBF16>(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5]));
-              w[c][q4].w = pack2<kBF16>(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7]));
-              if (!live) w[c][q4] = make_uint4(0, 0, 0, 0);
+              for (int q4 = 0; q4 < 4; ++q4) {
+                w[s][q4].x = pack2<kBF16>(__uint_as_float(r[8 * q4 + 0]), __uint_as_float(r[8 * q4 + 1]));
+                w[s][q4].y = pack2<kBF16>(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3]));
+                w[s][q4].z = pack2<kBF16>(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5]));
+                w[s][q4].w = pack2<kBF16>(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7]));
+                if (!live) w[s][q4] = make_uint4(0, 0, 0, 0);
+              }
+            } else {
+              uint32_t r[16];
+              tmem_ld16(o_addr, r);
+              tmem_ld_wait_for(r);
+#pragma unroll
+              for (int q4 = 0; q4 < 2; ++q4) {
+                w[s][q4].x = pack2<kBF16>(__uint_as_float(r[8 * q4 + 0]), __uint_as_float(r[8 * q4 + 1]));
+                w[s][q4].y = pack2<kBF16>(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3]));
+                w[s][q4].z = pack2<kBF16>(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5]));
+                w[s][q4].w = pack2<kBF16>(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7]));
+                if (!live) w[s][q4] = make_uint4(0, 0, 0, 0);
+              }
             }
           }
         }
@@ -775,16 +846,24 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kOEmpty));
-        if (n_mine > 0 && row < it.row_lim) {
+      }
 #pragma unroll
-          for (int c = 0; c < kDMine / 32; ++c) {
+      for (int s = 0; s < 2; ++s) {
+        const int row = it.q0 + 128 * s + lane_row;
+        if (row < it.row_lim) {
+          uint8_t* o_row = o_base + 2 * (int64_t)(128 * s + lane_row) * p.o_st;
+          if ((s == 0 ? n0 : n1) > 0) {
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(o_row + 64 * c + 16 * q4) = w[c][q4];
+            for (int q4 = 0; q4 < kDMine / 8; ++q4) *reinterpret_cast<uint4*>(o_row + 16 * q4) = w[s][q4];
+          } else {
+            // this tile is entirely padding: zero rows
+#pragma unroll
+            for (int q4 = 0; q4 < kDMine / 8; ++q4) *reinterpret_cast<uint4*>(o_row + 16 * q4) = make_uint4(0, 0, 0, 0);
           }
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(L::kItemEmpty + slot));
+      if (lane == 0) mbar_arrive(bar(L::kItemEmpty + islot));
     }
   }
 

@@ -12,6 +12,20 @@ namespace sigattn {
 // Device-side health word.  0 = fine.  A kernel that gives up on a bounded wait stores
 // (kernel_id << 16 | wait_site) here and unwinds instead of spinning forever.
 __device__ int g_status_word = 0;
+// Host-mapped copy of the word for this device (set once per device by the host side, may stay null):
+// written only when a wait is abandoned, so that the host can refuse further launches without
+// synchronising or copying anything in the normal case.
+__device__ volatile int* g_status_mirror = nullptr;
+
+__device__ __forceinline__ void record_abandoned_wait(int site) {
+  if (atomicCAS(&g_status_word, 0, site) == 0) {
+    volatile int* m = g_status_mirror;
+    if (m) {
+      *m = site;
+      __threadfence_system();
+    }
+  }
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -64,16 +78,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
-        atomicCAS(&g_status_word, 0, site);
+        record_abandoned_wait(site);
         return false;
       }
     }
   }
 }
 
-// The same for a converged warp: every lane waits, and the verdict is made warp-uniform.
+// The same for a converged warp: every lane waits, and the verdict is made warp-uniform.  The lanes of a
+// converged warp test the barrier in one access and get one answer, so the usual case - the phase is
+// already complete - returns without a vote; only a wait that has to spin pays for one.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, site)) != 0;
+  if (mbar_try_wait(bar, parity)) return true;
+  return __all_sync(__activemask(), mbar_wait(bar, parity, abort_flag, site)) != 0;
 }
 
 // ---------------------------------------------------------------- register re-allocation

@@ -11,6 +11,7 @@
 
 #include "../../include/sigattn_b200.h"
 #include "bwd_kernel.cuh"
+#include "bwd_stream_kernel.cuh"
 #include "f32_kernels.cuh"
 #include "fwd_kernel.cuh"
 
@@ -146,18 +147,45 @@ struct DeviceGuard {
   }
 };
 
+// Opt-in to the kernel's dynamic shared memory: once per kernel and device (`K` is a distinct type per
+// kernel signature only, so the flags are keyed by the kernel's address).
 template <typename K>
-int set_smem(K kernel, int bytes) {
+int set_smem(K kernel, int bytes, int device) {
+  constexpr int kMaxKernels = 64, kMaxDevices = 64;
+  static std::mutex mu;
+  static const void* seen[kMaxKernels] = {};
+  static bool done[kMaxKernels][kMaxDevices] = {};
+  if (device >= 0 && device < kMaxDevices) {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < kMaxKernels; ++i) {
+      if (seen[i] == nullptr) seen[i] = reinterpret_cast<const void*>(kernel);
+      if (seen[i] == reinterpret_cast<const void*>(kernel)) {
+        if (done[i][device]) return 0;
+        SIG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        done[i][device] = true;
+        return 0;
+      }
+    }
+  }
   SIG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   return 0;
 }
 
 // Work-item counters of the persistent kernels (forward and backward): a ring of (next item, finished CTAs) pairs.
 // Each launch takes the next pair; the kernel leaves its pair at zero when its last CTA finishes,
-// so a pair is only in doubt if more than kTicketSlots launches are in flight at once on
-// one device.
+// so a pair is only in doubt if more launches than the pool holds are in flight at once on one device.
+// Launches recorded into a stream capture keep their pair for every replay of the graph, so they draw
+// from a pool of their own that eager launches never touch.
 constexpr int kTicketSlots = 1024;
+constexpr int kEagerTicketSlots = 768;  // the remaining 256 serve launches made under stream capture
 __device__ unsigned int g_item_tickets[2 * kTicketSlots];
+
+// Host-visible copies of the devices' health words (see g_status_mirror in ptx.cuh): one page of this
+// library's own host data, pinned and mapped once per process.  A kernel writes its device's entry
+// only when it abandons a wait; every attention call reads it (a plain host load) before launching.
+constexpr int kMaxMirrorDevices = 64;
+alignas(4096) volatile int g_host_status[1024];
+bool g_host_status_mapped = false;
 
 struct FwdDeviceInfo {
   unsigned int* tickets = nullptr;
@@ -180,6 +208,25 @@ int fwd_device_info(int device, FwdDeviceInfo* out) {
     int n_sm = 0;
     SIG_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
     if (n_sm <= 0) return fail(-100, "device %d reports %d multiprocessors", device, n_sm);
+    // health-word mirror: best effort (without it failures are still reported by sigattn_device_status)
+    if (!g_host_status_mapped) {
+      if (cudaHostRegister(const_cast<int*>(g_host_status), sizeof(g_host_status),
+                           cudaHostRegisterPortable | cudaHostRegisterMapped) == cudaSuccess)
+        g_host_status_mapped = true;
+      else
+        (void)cudaGetLastError();
+    }
+    if (g_host_status_mapped && device < kMaxMirrorDevices) {
+      int* dev_view = nullptr;
+      if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev_view), const_cast<int*>(&g_host_status[device]), 0) ==
+              cudaSuccess && dev_view) {
+        volatile int* as_volatile = dev_view;
+        if (cudaMemcpyToSymbol(sigattn::g_status_mirror, &as_volatile, sizeof(as_volatile)) != cudaSuccess)
+          (void)cudaGetLastError();
+      } else {
+        (void)cudaGetLastError();
+      }
+    }
     cached[device].n_sm = n_sm;
     cached[device].tickets = ptr;
   }
@@ -187,14 +234,25 @@ int fwd_device_info(int device, FwdDeviceInfo* out) {
   return 0;
 }
 
+// Non-zero when a kernel of this library has abandoned a wait on `device` and nobody has read the
+// failure yet (sigattn_device_status reads and clears it).
+int pending_failure(int device) {
+  if (device < 0 || device >= kMaxMirrorDevices) return 0;
+  return g_host_status[device];
+}
+#define SIG_REFUSE_IF_SICK(p)                                                                               \
+  do {                                                                                                      \
+    if (int site_ = pending_failure((p)->device))                                                           \
+      return fail(-5, "device %d: a kernel gave up on a bounded wait (site 0x%x); results since then are "  \
+                      "undefined and launches are refused until sigattn_device_status() has been called",   \
+                  (p)->device, site_);                                                                      \
+  } while (0)
+
 // (batch, head) pairs per scheduling group of the persistent kernels.  Under a causal mask the items of
 // one head differ in weight, and handing out the heavy items of many heads first balances the CTAs; the
 // group is limited so that what its heads stream per item (`bytes_per_head`) stays within the L2.
 // Without a causal mask the plain order is kept.
 int schedule_group(bool causal, int64_t n_bh, int64_t bytes_per_head, int64_t l2_budget) {
-#ifdef SIG_SCHEDULE_GROUP
-  return SIG_SCHEDULE_GROUP;
-#endif
   if (!causal || n_bh <= 1) return 1;
   int64_t g = l2_budget / (bytes_per_head > 0 ? bytes_per_head : 1);
   if (g < 1) g = 1;
@@ -202,18 +260,24 @@ int schedule_group(bool causal, int64_t n_bh, int64_t bytes_per_head, int64_t l2
   return (int)g;
 }
 
-// The pair of counters for one launch.
-unsigned int* next_ticket_pair(const FwdDeviceInfo& info, int device) {
-  static std::atomic<unsigned int> next_slot[64];
-  return info.tickets + 2 * (next_slot[device].fetch_add(1u) % kTicketSlots);
+// The pair of counters for one launch on `stream`.
+unsigned int* next_ticket_pair(const FwdDeviceInfo& info, int device, cudaStream_t stream) {
+  static std::atomic<unsigned int> next_eager[64], next_captured[64];
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    st = cudaStreamCaptureStatusNone;
+  }
+  if (st == cudaStreamCaptureStatusNone) return info.tickets + 2 * (next_eager[device].fetch_add(1u) % kEagerTicketSlots);
+  return info.tickets + 2 * (kEagerTicketSlots + next_captured[device].fetch_add(1u) % (kTicketSlots - kEagerTicketSlots));
 }
 
-template <int D, bool kBF16, bool kScoreMod>
+template <int D, bool kBF16, bool kScoreMod, bool kAccurate>
 int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm) {
   using namespace sigattn;
-  auto kernel = sigattn_fwd_kernel<D, kBF16, kScoreMod>;
+  auto kernel = sigattn_fwd_kernel<D, kBF16, kScoreMod, kAccurate>;
   constexpr int smem = FwdSmem<D>::kDynBytes;
-  if (int rc = set_smem(kernel, smem)) return rc;
+  if (int rc = set_smem(kernel, smem, p->device)) return rc;
   FwdParams fp;
   fp.o = p->o;
   fp.o_sb = p->o_strides[0];
@@ -240,7 +304,7 @@ int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   fp.group = schedule_group(fp.causal != 0, (int64_t)p->B * p->H, (int64_t)p->Tk * D * 2 * 2, 64ll << 20);
   FwdDeviceInfo info;
   if (int rc = fwd_device_info(p->device, &info)) return rc;
-  fp.ticket = next_ticket_pair(info, p->device);
+  fp.ticket = next_ticket_pair(info, p->device, static_cast<cudaStream_t>(p->stream));
   // persistent: one CTA per SM (the kernel's shared memory allows no more), fewer when there are fewer items
   dim3 grid((unsigned int)std::min<int64_t>(n_items, info.n_sm));
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
@@ -251,9 +315,10 @@ int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   return 0;
 }
 
-template <int D, bool kBF16>
-int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
-               const CUtensorMap& dom) {
+// The default backward: the fused 5-GEMM kernel with fp32 dQ reductions into a workspace (bwd_kernel.cuh).
+template <int D, bool kBF16, bool kAccurate>
+int launch_bwd_fused(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
+                     const CUtensorMap& dom) {
   using namespace sigattn;
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   const Extents ex = extents(p);
@@ -289,12 +354,12 @@ int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   bp.group = schedule_group(bp.causal != 0, (int64_t)p->B * p->H, (int64_t)p->Tq * D * (2 + 2 + 4), 32ll << 20);
   FwdDeviceInfo info;
   if (int rc = fwd_device_info(p->device, &info)) return rc;
-  bp.ticket = next_ticket_pair(info, p->device);
+  bp.ticket = next_ticket_pair(info, p->device, stream);
 
   {
-    auto kernel = sigattn_bwd_kernel<D, kBF16>;
+    auto kernel = sigattn_bwd_kernel<D, kBF16, kAccurate>;
     constexpr int smem = BwdSmem<D>::kDynBytes;
-    if (int rc = set_smem(kernel, smem)) return rc;
+    if (int rc = set_smem(kernel, smem, p->device)) return rc;
     // persistent: one CTA per SM (the kernel's shared memory allows no more), fewer when there are fewer items
     dim3 grid((unsigned int)std::min<int64_t>(n_items, info.n_sm));
     if (p->ev_main_start) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream));
@@ -317,6 +382,62 @@ int launch_bwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
     sigattn_dq_convert_kernel<D, kBF16><<<blocks, threads, 0, stream>>>(cp);
     SIG_CUDA(cudaGetLastError());
   }
+  return 0;
+}
+
+// The split backward (SIGATTN_BWD_SPLIT): the streaming kernel of bwd_stream_kernel.cuh, once in dK/dV mode
+// and once in dQ mode.  No workspace, no atomics, deterministic.
+template <int D, bool kBF16, bool kDKV, bool kAccurate>
+int launch_bwd_stream_mode(const SigAttnParams* p, const CUtensorMap& r1, const CUtensorMap& r2, const CUtensorMap& c1,
+                           const CUtensorMap& c2, const FwdDeviceInfo& info) {
+  using namespace sigattn;
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  BwdStreamParams bp;
+  if (kDKV) {
+    bp.out1 = p->dk; bp.o1_sb = p->dk_strides[0]; bp.o1_st = p->dk_strides[1]; bp.o1_sh = p->dk_strides[2];
+    bp.out2 = p->dv; bp.o2_sb = p->dv_strides[0]; bp.o2_st = p->dv_strides[1]; bp.o2_sh = p->dv_strides[2];
+    bp.lens_r = p->seq_lens_k; bp.lens_c = p->seq_lens_q;
+    bp.cu_r = p->cu_seqlens_k; bp.cu_c = p->cu_seqlens_q;
+    bp.Tr = p->Tk; bp.Tc = p->Tq;
+  } else {
+    bp.out1 = p->dq; bp.o1_sb = p->dq_strides[0]; bp.o1_st = p->dq_strides[1]; bp.o1_sh = p->dq_strides[2];
+    bp.out2 = nullptr; bp.o2_sb = bp.o2_st = bp.o2_sh = 0;
+    bp.lens_r = p->seq_lens_q; bp.lens_c = p->seq_lens_k;
+    bp.cu_r = p->cu_seqlens_q; bp.cu_c = p->cu_seqlens_k;
+    bp.Tr = p->Tq; bp.Tc = p->Tk;
+  }
+  bp.bias = p->bias;
+  bp.score_mod = p->score_mod;
+  bp.scale = p->scale;
+  bp.bias_scalar = p->bias_scalar;
+  bp.B = p->B; bp.H = p->H; bp.Tk = p->Tk;
+  bp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
+  bp.n_rblk = (bp.Tr + kBsTile - 1) / kBsTile;
+  const int64_t n_items = (int64_t)bp.n_rblk * p->H * p->B;
+  if (n_items > INT32_MAX) return fail(-2, "too many (batch, head, tile) items: %lld", (long long)n_items);
+  bp.n_items = (int)n_items;
+  // what one head streams per item (the two streamed tensors), half of the L2 for a group
+  bp.group = schedule_group(bp.causal != 0, (int64_t)p->B * p->H, (int64_t)bp.Tc * D * 2 * 2, 64ll << 20);
+  bp.ticket = next_ticket_pair(info, p->device, stream);
+  auto kernel = sigattn_bwd_stream_kernel<D, kBF16, kDKV, kAccurate>;
+  constexpr int smem = BsSmem<D, kDKV>::kDynBytes;
+  if (int rc = set_smem(kernel, smem, p->device)) return rc;
+  dim3 grid((unsigned int)std::min<int64_t>(n_items, info.n_sm));
+  kernel<<<grid, kBsThreads, smem, stream>>>(r1, r2, c1, c2, bp);
+  SIG_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <int D, bool kBF16, bool kAccurate>
+int launch_bwd_stream(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm,
+                      const CUtensorMap& dom) {
+  FwdDeviceInfo info;
+  if (int rc = fwd_device_info(p->device, &info)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  if (p->ev_main_start) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream));
+  if (int rc = launch_bwd_stream_mode<D, kBF16, true, kAccurate>(p, km, vm, qm, dom, info)) return rc;
+  if (int rc = launch_bwd_stream_mode<D, kBF16, false, kAccurate>(p, qm, dom, km, vm, info)) return rc;
+  if (p->ev_main_stop) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_stop), stream));
   return 0;
 }
 
@@ -382,14 +503,14 @@ int launch_f32_d(const SigAttnParams* p, bool backward) {
   if (p->ev_main_start) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream));
   if (!backward) {
     auto kernel = sigattn_fwd_f32_kernel<D>;
-    if (int rc = set_smem(kernel, F32Smem<D>::kFwdBytes)) return rc;
+    if (int rc = set_smem(kernel, F32Smem<D>::kFwdBytes, p->device)) return rc;
     kernel<<<dim3(n_q, p->H, p->B), kF32Threads, F32Smem<D>::kFwdBytes, stream>>>(fp);
     SIG_CUDA(cudaGetLastError());
   } else {
     auto kdkdv = sigattn_bwd_dkdv_f32_kernel<D>;
     auto kdq = sigattn_bwd_dq_f32_kernel<D>;
-    if (int rc = set_smem(kdkdv, F32Smem<D>::kDkdvBytes)) return rc;
-    if (int rc = set_smem(kdq, F32Smem<D>::kDqBytes)) return rc;
+    if (int rc = set_smem(kdkdv, F32Smem<D>::kDkdvBytes, p->device)) return rc;
+    if (int rc = set_smem(kdq, F32Smem<D>::kDqBytes, p->device)) return rc;
     kdkdv<<<dim3(n_k, p->H, p->B), kF32Threads, F32Smem<D>::kDkdvBytes, stream>>>(fp);
     SIG_CUDA(cudaGetLastError());
     kdq<<<dim3(n_q, p->H, p->B), kF32Threads, F32Smem<D>::kDqBytes, stream>>>(fp);
@@ -469,6 +590,7 @@ int sigattn_device_status(int device) {
     SIG_CUDA(cudaGetSymbolAddress(&tickets, g_item_tickets));
     SIG_CUDA(cudaMemset(tickets, 0, sizeof(unsigned int) * 2 * kTicketSlots));
   }
+  if (device >= 0 && device < kMaxMirrorDevices) g_host_status[device] = 0;
   return v;
 }
 
@@ -478,6 +600,10 @@ int sigattn_selftest_bounded_wait(int device, int limit_ms) {
   if (limit_ms < 1 || limit_ms > 1000) return fail(-2, "limit_ms must be in [1, 1000], got %d", limit_ms);
   DeviceGuard g;
   SIG_CUDA(g.enter(device));
+  {
+    FwdDeviceInfo info;  // first use of the device: also installs the host-visible copy of the health word
+    if (int rc = fwd_device_info(device, &info)) return rc;
+  }
   int* flag = nullptr;
   SIG_CUDA(cudaMalloc(&flag, sizeof(int)));
   cudaError_t e = cudaMemset(flag, 0xff, sizeof(int));
@@ -497,6 +623,7 @@ int sigattn_fwd(const SigAttnParams* p) {
   int rc = check_common(p, false);
   if (rc < 0) return rc;
   if (rc == 1) return 0;
+  SIG_REFUSE_IF_SICK(p);
   DeviceGuard g;
   SIG_CUDA(g.enter(p->device));
   const Extents ex = extents(p);
@@ -516,7 +643,12 @@ int sigattn_fwd(const SigAttnParams* p) {
 
   const bool bf = p->dtype == SIGATTN_BF16;
   const bool sm = p->score_mod != nullptr;
-#define SIG_FWD(DD, BF, SM) return launch_fwd<DD, BF, SM>(p, qm, km, vm)
+  const bool acc = (p->flags & SIGATTN_ACCURATE) != 0;
+#define SIG_FWD(DD, BF, SM)                                             \
+  do {                                                                  \
+    if (acc) return launch_fwd<DD, BF, SM, true>(p, qm, km, vm);        \
+    return launch_fwd<DD, BF, SM, false>(p, qm, km, vm);                \
+  } while (0)
   if (p->D == 64) {
     if (bf) { if (sm) SIG_FWD(64, true, true); else SIG_FWD(64, true, false); }
     else    { if (sm) SIG_FWD(64, false, true); else SIG_FWD(64, false, false); }
@@ -533,6 +665,7 @@ int sigattn_bwd(const SigAttnParams* p) {
   int rc = check_common(p, true);
   if (rc < 0) return rc;
   if (rc == 1) return 0;
+  SIG_REFUSE_IF_SICK(p);
   DeviceGuard g;
   SIG_CUDA(g.enter(p->device));
   const Extents ex = extents(p);
@@ -556,8 +689,22 @@ int sigattn_bwd(const SigAttnParams* p) {
     for (int i = ex.packed ? 1 : 0; i < 3; ++i)
       if (ostr[t][i] % 8 != 0) return fail(-3, "gradient strides must be multiples of 8 elements");
   }
-  if (p->D == 64) return p->dtype == SIGATTN_BF16 ? launch_bwd<64, true>(p, qm, km, vm, dom) : launch_bwd<64, false>(p, qm, km, vm, dom);
-  return p->dtype == SIGATTN_BF16 ? launch_bwd<128, true>(p, qm, km, vm, dom) : launch_bwd<128, false>(p, qm, km, vm, dom);
+  const bool bf = p->dtype == SIGATTN_BF16;
+  const bool acc = (p->flags & SIGATTN_ACCURATE) != 0;
+  const bool split = (p->flags & SIGATTN_BWD_SPLIT) != 0;
+#define SIG_BWD(DD, BF)                                                                   \
+  do {                                                                                    \
+    if (split) {                                                                          \
+      if (acc) return launch_bwd_stream<DD, BF, true>(p, qm, km, vm, dom);                \
+      return launch_bwd_stream<DD, BF, false>(p, qm, km, vm, dom);                        \
+    }                                                                                     \
+    if (acc) return launch_bwd_fused<DD, BF, true>(p, qm, km, vm, dom);                   \
+    return launch_bwd_fused<DD, BF, false>(p, qm, km, vm, dom);                           \
+  } while (0)
+  if (p->D == 64) { if (bf) SIG_BWD(64, true); else SIG_BWD(64, false); }
+  else            { if (bf) SIG_BWD(128, true); else SIG_BWD(128, false); }
+#undef SIG_BWD
+  return fail(-2, "unreachable");
 }
 
 int sigattn_bwd_static_scratch(const SigAttnParams* p) {
@@ -568,6 +715,8 @@ int sigattn_bwd_static_scratch(const SigAttnParams* p) {
   const Extents ex = extents(p);
   const unsigned long long elems = (unsigned long long)ex.B * (unsigned long long)ex.Tq * (unsigned long long)p->H *
                                    (unsigned long long)p->D;
+  // float32 tensors run the exact kernels, which use no accumulator: no limit applies to them
+  if (p->dtype == SIGATTN_FP32) return sigattn_bwd(p);
   if (elems > SIGATTN_STATIC_SCRATCH_ELEMS)
     return fail(-4, "problem too large for the built-in scratch: B*Tq*H*D = %llu elements, limit %u; "
                     "use sigattn_bwd with a caller-provided workspace", elems, (unsigned)SIGATTN_STATIC_SCRATCH_ELEMS);
@@ -579,6 +728,7 @@ int sigattn_bwd_static_scratch(const SigAttnParams* p) {
   }
   // Same path as sigattn_bwd from here on; it zero-fills the accumulator on p->stream first.
   SigAttnParams q = *p;
+  q.flags &= ~(uint32_t)SIGATTN_BWD_SPLIT;  // the kernel that accumulates dQ in scratch memory
   q.workspace = scratch;
   q.workspace_bytes = (size_t)SIGATTN_STATIC_SCRATCH_ELEMS * sizeof(float);
   return sigattn_bwd(&q);

@@ -12,8 +12,10 @@ All arithmetic happens in the CUDA library; nothing here computes attention.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -28,19 +30,99 @@ _DEVICE_OK: dict = {}
 
 
 def _require_b200(dev: torch.device) -> None:
-    """The kernels exist for sm_100 only; anything else is an error, never a fallback."""
+    """The kernels are built for sm_100a only (code that is not forward compatible, not even with
+    other 10.x parts); anything else is an error, never a fallback."""
     if dev.type != "cuda":
         raise RuntimeError(f"triton_sigmoid_b200 runs on CUDA tensors only, got device '{dev}'")
     idx = dev.index if dev.index is not None else torch.cuda.current_device()
     ok = _DEVICE_OK.get(idx)
     if ok is None:
         major, minor = torch.cuda.get_device_capability(idx)
-        ok = _DEVICE_OK[idx] = major == 10
-        if not ok:
-            _DEVICE_OK[idx] = False
-    if not _DEVICE_OK[idx]:
+        ok = _DEVICE_OK[idx] = (major, minor) == (10, 0)
+    if not ok:
         major, minor = torch.cuda.get_device_capability(idx)
         raise RuntimeError(f"triton_sigmoid_b200 requires an sm_100 GPU (B200), found sm_{major}{minor}")
+
+
+# ----------------------------------------------------------------------------- run-time switches
+_TRUE = ("1", "true", "yes", "on")
+_accurate_override: Optional[bool] = None
+
+
+def _accurate() -> bool:
+    """Accurate-sigmoid mode: the reference's ``TRITON_SIGMOID_ACCURATE`` environment switch (same
+    accepted values, ``src/triton_sigmoid/kernel_utils.py:190-193``), read when an op runs rather than at
+    import, unless :func:`accurate_sigmoid` overrides it."""
+    if _accurate_override is not None:
+        return _accurate_override
+    return os.environ.get("TRITON_SIGMOID_ACCURATE", "").lower() in _TRUE
+
+
+@contextlib.contextmanager
+def accurate_sigmoid(enabled: Optional[bool] = True):
+    """Within the block, run the tensor-core kernels with the accurate sigmoid (``True``), the default fast
+    one (``False``), or whatever the environment says (``None``)."""
+    global _accurate_override
+    prev, _accurate_override = _accurate_override, enabled
+    try:
+        yield
+    finally:
+        _accurate_override = prev
+
+
+def _debug_sync() -> bool:
+    """``SIGATTN_B200_DEBUG=1``: synchronise after every launch and raise at once if a kernel gave up on a
+    bounded wait (outputs are poison-filled beforehand so that unwritten rows show)."""
+    return os.environ.get("SIGATTN_B200_DEBUG", "").lower() in _TRUE
+
+
+def device_status(device=None) -> int:
+    """Synchronise `device` and return its health word: 0, or the code of the bounded wait a kernel of this
+    library gave up on since the last call (reading a failure clears it, after which the library is usable
+    again; results of launches made in between are undefined)."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    rc = _cabi.load().sigattn_device_status(idx if idx is not None else torch.cuda.current_device())
+    if rc < 0:
+        raise RuntimeError(f"sigattn_device_status failed (code {rc}): {_cabi.last_error()}")
+    return rc
+
+
+def _bwd_split() -> bool:
+    """``SIGATTN_B200_BWD_SPLIT=1`` selects the pair of streaming backward kernels (7 GEMMs per tile pair, no
+    workspace, no atomics, run-to-run deterministic gradients) instead of the default fused kernel (5 GEMMs,
+    dQ accumulated with fp32 reductions into a workspace), which was measured faster."""
+    return os.environ.get("SIGATTN_B200_BWD_SPLIT", "").lower() in _TRUE
+
+
+def _flags(is_causal: bool) -> int:
+    return (_cabi.SIGATTN_CAUSAL if is_causal else 0) | (_cabi.SIGATTN_ACCURATE if _accurate() else 0)
+
+
+def _bwd_workspace(p, lib, B, Tq, H, D, device):
+    """The fused backward's fp32 dQ accumulator; the split backward needs none (and gets its flag here)."""
+    if _bwd_split():
+        p.flags |= _cabi.SIGATTN_BWD_SPLIT
+        return None
+    ws_bytes = lib.sigattn_bwd_workspace_bytes(B, Tq, H, D)
+    ws = torch.empty(max(ws_bytes, 16) // 4, dtype=torch.float32, device=device)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * 4
+    return ws
+
+
+def _launch(fn, p, what: str, outputs) -> None:
+    """One C-ABI call.  A kernel that gave up on a wait earlier makes the call itself fail (the library
+    keeps a host-visible copy of the health word), which surfaces here as RuntimeError; in debug mode the
+    device is synchronised and checked after the launch as well."""
+    debug = _debug_sync()
+    if debug:
+        for t in outputs:
+            t.fill_(float("nan"))
+    _cabi.check(fn(ctypes.byref(p)), what)
+    if debug:
+        code = device_status(torch.device("cuda", p.device))
+        if code != 0:
+            raise RuntimeError(f"{what}: a kernel gave up on a bounded wait (site 0x{code:x}); its outputs are "
+                               "undefined.  The health word has been cleared, the library is usable again.")
 
 
 def _strides3(t: torch.Tensor):
@@ -55,7 +137,7 @@ def _base_params(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_cau
     p.struct_bytes = ctypes.sizeof(_cabi.SigAttnParams)
     p.dtype = _DTYPE_CODE[q.dtype]
     p.B, p.H, p.D, p.Tq, p.Tk = B, H, D, Tq, k.shape[1]
-    p.flags = _cabi.SIGATTN_CAUSAL if is_causal else 0
+    p.flags = _flags(is_causal)
     p.scale = float(scale)
     p.bias_scalar = 0.0
     p.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
@@ -101,7 +183,7 @@ def _run_fwd(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal)
     p = _base_params(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal)
     p.o = out.data_ptr()
     p.o_strides = _strides3(out)
-    _cabi.check(_cabi.load().sigattn_fwd(ctypes.byref(p)), "sigattn_fwd")
+    _launch(_cabi.load().sigattn_fwd, p, "sigattn_fwd", (out,))
     return out
 
 
@@ -114,16 +196,13 @@ def _run_bwd(q, k, v, do, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_cau
     bias, score_mod, seq_lens_q, seq_lens_k = _prep_aux(q, bias, score_mod, seq_lens_q, seq_lens_k)
     lib = _cabi.load()
     B, Tq, H, D = q.shape
-    ws_bytes = lib.sigattn_bwd_workspace_bytes(B, Tq, H, D)
-    ws = torch.empty(max(ws_bytes, 16) // 4, dtype=torch.float32, device=q.device)
     p = _base_params(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal)
     p.dout = do.data_ptr()
     p.do_strides = _strides3(do)
     p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     p.dq_strides, p.dk_strides, p.dv_strides = _strides3(dq), _strides3(dk), _strides3(dv)
-    p.workspace = ws.data_ptr()
-    p.workspace_bytes = ws.numel() * 4
-    _cabi.check(lib.sigattn_bwd(ctypes.byref(p)), "sigattn_bwd")
+    ws = _bwd_workspace(p, lib, B, Tq, H, D, q.device)  # noqa: F841  (kept alive until the launch is queued)
+    _launch(lib.sigattn_bwd, p, "sigattn_bwd", (dq, dk, dv))
     return dq, dk, dv
 
 
@@ -223,7 +302,7 @@ def _varlen_params(q, k, v, cu_q, cu_k, max_q, max_k, bias, score_mod, scale, is
     p.struct_bytes = ctypes.sizeof(_cabi.SigAttnParams)
     p.dtype = _DTYPE_CODE[q.dtype]
     p.B, p.H, p.D, p.Tq, p.Tk = cu_q.numel() - 1, H, D, int(max_q), int(max_k)
-    p.flags = _cabi.SIGATTN_CAUSAL if is_causal else 0
+    p.flags = _flags(is_causal)
     p.scale = float(scale)
     p.bias_scalar = 0.0
     p.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
@@ -253,7 +332,9 @@ def sigmoid_attn_varlen_fwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor
                                score_mod: Optional[torch.Tensor], sm_scale: float, is_causal: bool) -> torch.Tensor:
     _check_varlen_kernel_inputs(Q, K, V)
     Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
-    out = torch.empty_like(Q)
+    # only rows of the sequences are written: rows between or behind them, and rows of a sequence beyond
+    # max_seqlen_q, stay zero (as in the backward)
+    out = torch.zeros_like(Q)
     if out.numel() == 0:
         return out
     bias, score_mod, _, _ = _prep_aux(Q, bias, score_mod, None, None)
@@ -262,6 +343,8 @@ def sigmoid_attn_varlen_fwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor
     p.o = out.data_ptr()
     p.o_strides = (ctypes.c_int64 * 3)(0, out.stride(0), out.stride(1))
     _cabi.check(_cabi.load().sigattn_fwd(ctypes.byref(p)), "sigattn_fwd")
+    if _debug_sync() and device_status(Q.device) != 0:
+        raise RuntimeError("sigattn_fwd: a kernel gave up on a bounded wait; its outputs are undefined")
     return out
 
 
@@ -284,16 +367,16 @@ def sigmoid_attn_varlen_bwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor
     bias, score_mod, _, _ = _prep_aux(Q, bias, score_mod, None, None)
     lib = _cabi.load()
     total_q, H, D = Q.shape
-    ws_bytes = lib.sigattn_bwd_workspace_bytes(1, total_q, H, D)
-    ws = torch.empty(max(ws_bytes, 16) // 4, dtype=torch.float32, device=Q.device)
     p = _varlen_params(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, bias, score_mod, sm_scale,
                        is_causal)
     s3 = lambda t: (ctypes.c_int64 * 3)(0, t.stride(0), t.stride(1))
     p.dout, p.do_strides = dO.data_ptr(), s3(dO)
     p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     p.dq_strides, p.dk_strides, p.dv_strides = s3(dq), s3(dk), s3(dv)
-    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * 4
+    ws = _bwd_workspace(p, lib, 1, total_q, H, D, Q.device)  # noqa: F841
     _cabi.check(lib.sigattn_bwd(ctypes.byref(p)), "sigattn_bwd")
+    if _debug_sync() and device_status(Q.device) != 0:
+        raise RuntimeError("sigattn_bwd: a kernel gave up on a bounded wait; its outputs are undefined")
     return dq, dk, dv
 
 

@@ -20,9 +20,10 @@ def _event() -> torch.cuda.Event:
 
 
 def time_main_kernel(direction: str, q, k, v, dout=None, seq_lens_q=None, seq_lens_k=None, bias=None, scale=None,
-                     is_causal=False, iters: int = 10, flush: Optional[torch.Tensor] = None) -> List[float]:
-    """Milliseconds of the main kernel of `iters` calls of sigattn_fwd ("fwd") or sigattn_bwd
-    ("bwd").  If `flush` is given it is zero-filled between calls (L2 flush)."""
+                     is_causal=False, iters: int = 10, flush: Optional[torch.Tensor] = None, split_bwd: bool = False) -> List[float]:
+    """Milliseconds of the main kernel(s) of `iters` calls of sigattn_fwd ("fwd") or sigattn_bwd
+    ("bwd": the fused kernel alone, or the two streaming kernels when `split_bwd`).  If `flush` is given it
+    is zero-filled between calls (L2 flush)."""
     _check_kernel_inputs(q, k, v)
     B, Tq, H, D = q.shape
     Tk = k.shape[1]
@@ -41,14 +42,18 @@ def time_main_kernel(direction: str, q, k, v, dout=None, seq_lens_q=None, seq_le
         keep.append(out)
     elif direction == "bwd":
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        ws = torch.empty(max(lib.sigattn_bwd_workspace_bytes(B, Tq, H, D), 16) // 4, dtype=torch.float32,
-                         device=q.device)
         p.dout, p.do_strides = dout.data_ptr(), _strides3(dout)
         p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
         p.dq_strides, p.dk_strides, p.dv_strides = _strides3(dq), _strides3(dk), _strides3(dv)
-        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * 4
+        keep += [dq, dk, dv]
+        if split_bwd:
+            p.flags |= _cabi.SIGATTN_BWD_SPLIT
+        else:
+            ws = torch.empty(max(lib.sigattn_bwd_workspace_bytes(B, Tq, H, D), 16) // 4, dtype=torch.float32,
+                             device=q.device)
+            p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel() * 4
+            keep.append(ws)
         call = lib.sigattn_bwd
-        keep += [dq, dk, dv, ws]
     else:
         raise ValueError("direction must be 'fwd' or 'bwd'")
     pairs = []
