@@ -14,8 +14,13 @@ FLOP accounting (the reference's benchmark): forward 4 B H N^2 D, halved when ca
 4 H D sum_b Lq_b Lk_b; backward 2.5x forward; forward+backward 3.5x.
 
 Rank 0 prints ONE JSON line.  `value` is forward+backward TFLOP/s with inputs resident in HBM;
-`e2e` is the same metric with pinned HOST inputs and outputs, the copies inside the timed region;
+`e2e` is the same metric with pinned HOST inputs and outputs, the copies inside the timed region (one
+batch element at a time over three streams, so that the upload of element b+1 and the download of
+element b-1 run under the computation of element b);
 `roofline` is the backward kernel (the dominant one) timed alone through the C ABI's event hooks;
+`extra.workloads` holds device-timed forward and forward+backward figures of the other configurations
+(causal variant, padded, the dense causal D=128 configuration - sharded over the ranks under torchrun -
+and two sequence-length sweep points), a few steps each;
 `cpu_baseline` is the reference's own PyTorch CPU code timed on the host cores (rank 0, N=1).
 
 --impl reference runs the unmodified reference package (its Triton kernels, installed under
@@ -207,21 +212,51 @@ def timed(fn, steps: int, warmup: int, flush, barrier) -> float:
 
 
 def e2e_step_factory(w, fns, q, k, v, do, lens):
-    """Step with pinned host inputs/outputs: H2D of q,k,v,dO, forward+backward, D2H of O,dQ,dK,dV."""
+    """Step with pinned host inputs/outputs, what a caller whose tensors live on the host would do: per batch
+    element, H2D of q,k,v,dO on a copy stream, forward+backward on the compute stream, D2H of O,dQ,dK,dV on
+    a third stream, chained by events, so uploads, computation and downloads of neighbouring elements overlap.
+    Returns (step, bytes in, bytes out); `step` leaves the current stream waiting for every download."""
     host_in = [t.detach().cpu().pin_memory() for t in (q, k, v, do)]
     host_out = [torch.empty_like(t).pin_memory() for t in host_in]
     dense, padded, _ = fns
+    dev = q.device
+    B = q.shape[0]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
     def step():
-        dq_, dk_, dv_, ddo = [t.to(q.device, non_blocking=True) for t in host_in]
-        dq_.requires_grad_(), dk_.requires_grad_(), dv_.requires_grad_()
-        if w["padded"]:
-            o = padded(dq_, dk_, dv_, seq_lens_k=lens, seq_lens_q=lens, is_causal=w["causal"])
-        else:
-            o = dense(dq_, dk_, dv_, is_causal=w["causal"])
-        o.backward(ddo)
-        for dst, src in zip(host_out, (o.detach(), dq_.grad, dk_.grad, dv_.grad)):
-            dst.copy_(src, non_blocking=True)
+        main = torch.cuda.current_stream(dev)
+        start = torch.cuda.Event()
+        start.record(main)
+        s_in.wait_event(start)
+        s_out.wait_event(start)
+        staged = []
+        for b in range(B):
+            with torch.cuda.stream(s_in):
+                xs = [t[b:b + 1].to(dev, non_blocking=True) for t in host_in]
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+            staged.append((xs, ev))
+        for b, (xs, ev) in enumerate(staged):
+            main.wait_event(ev)
+            qb, kb, vb, dob = xs
+            for t in xs:
+                t.record_stream(main)
+            qb.requires_grad_(), kb.requires_grad_(), vb.requires_grad_()
+            if w["padded"]:
+                lb = lens[b:b + 1]
+                o = padded(qb, kb, vb, seq_lens_k=lb, seq_lens_q=lb, is_causal=w["causal"])
+            else:
+                o = dense(qb, kb, vb, is_causal=w["causal"])
+            o.backward(dob)
+            done = torch.cuda.Event()
+            done.record(main)
+            outs = (o.detach(), qb.grad, kb.grad, vb.grad)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for dst, src in zip(host_out, outs):
+                    src.record_stream(s_out)
+                    dst[b:b + 1].copy_(src, non_blocking=True)
+        main.wait_stream(s_out)
 
     nbytes = sum(t.numel() * t.element_size() for t in host_in)
     return step, nbytes, nbytes
@@ -278,6 +313,94 @@ def cpu_baseline(w: dict, budget_s: float = 20.0) -> dict:
 
 
 # ----------------------------------------------------------------------------- main
+# Other configurations recorded (device-timed, a few steps each) in `extra.workloads` of the JSON line.
+EXTRA_WORKLOADS = ["cfg2-causal", "cfg3", "cfg3-causal", "cfg4", "sweep:512:64:bf16:dense:full",
+                   "sweep:32768:64:bf16:dense:full", "sweep:8192:128:bf16:dense:full"]
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the named kernel on the default
+# workload (dense fp16, B=4, N=4096, H=16, D=64), from an `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum
+# --clock-control none -k regex:<kernel> -c 1` capture of this very launch; None = not captured for the
+# current kernels.  Only reported for that workload on one GPU.
+NCU_DRAM_BYTES_DEFAULT_WORKLOAD = {"sigattn_bwd_kernel": None, "sigattn_fwd_kernel": None}
+
+
+class Dist:
+    """torch.distributed when launched under torchrun, no-ops otherwise."""
+
+    def __init__(self, device):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.device = device
+        self.pg = None
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.init_process_group("nccl", device_id=device)
+            self.pg = dist
+
+    def barrier(self):
+        if self.pg is not None:
+            self.pg.barrier()
+
+    def _reduce(self, x: float, op) -> float:
+        if self.pg is None:
+            return x
+        t = torch.tensor([x], device=self.device, dtype=torch.float64)
+        self.pg.all_reduce(t, op=op)
+        return float(t.item())
+
+    def max(self, x: float) -> float:
+        return self._reduce(x, self.pg.ReduceOp.MAX if self.pg else None)
+
+    def sum(self, x: float) -> float:
+        return self._reduce(x, self.pg.ReduceOp.SUM if self.pg else None)
+
+    def close(self):
+        if self.pg is not None:
+            self.pg.destroy_process_group()
+
+
+def setup_workload(w, device, d: Dist):
+    """Tensors of this rank: its own data (weak scaling) or its shard of the one problem (strong scaling)."""
+    strong = bool(w.get("strong")) and d.world > 1
+    if strong:
+        from triton_sigmoid_b200.launcher import plan_shard, take_shard
+
+        sh = plan_shard(w["B"], w["H"], d.world, d.rank)
+        q, k, v, do, lens = make_data(w, device, 0)
+        q, k, v, do = [take_shard(t, sh).contiguous() for t in (q, k, v, do)]
+        if lens is not None:
+            lens = take_shard(lens, sh, None).contiguous()
+        wl = dict(w, B=sh.b1 - sh.b0, H=sh.h1 - sh.h0)
+    else:
+        q, k, v, do, lens = make_data(w, device, d.rank)
+        wl = w
+    for t in (q, k, v):
+        t.requires_grad_()
+    return wl, strong, q, k, v, do, lens
+
+
+def measure_extra(name, fns, device, d: Dist, flush, pk) -> dict:
+    """Forward and forward+backward of one more configuration, 3 warm-up + 3 timed steps each, device-timed,
+    max over ranks, whole-job FLOPs."""
+    w = parse_workload(name)
+    wl, strong, q, k, v, do, lens = setup_workload(w, device, d)
+    F_total = d.sum(fwd_flops(wl, lens))
+    fwd_only, fwd_bwd = make_step(wl, fns, q, k, v, do, lens)
+    ms_fb = d.max(timed(fwd_bwd, 3, 3, flush, d.barrier)) / 3
+    ms_f = d.max(timed(fwd_only, 3, 3, flush, d.barrier)) / 3
+    q.grad = k.grad = v.grad = None
+    res = {"B_per_gpu": wl["B"], "N": w["N"], "H_per_gpu": wl["H"], "D": w["D"], "dtype": w["dtype"], "causal": w["causal"],
+           "padded": w["padded"], "scaling": "strong" if strong else "weak",
+           "fwd_tflops": F_total / (ms_f * 1e-3) / 1e12, "fwd_bwd_tflops": 3.5 * F_total / (ms_fb * 1e-3) / 1e12,
+           "fwd_ms": ms_f, "fwd_bwd_ms": ms_fb}
+    res["fwd_frac_of_peak"] = res["fwd_tflops"] / (pk["burst"] * d.world)
+    res["fwd_bwd_frac_of_peak"] = res["fwd_bwd_tflops"] / (pk["burst"] * d.world)
+    del q, k, v, do, lens, fwd_only, fwd_bwd
+    torch.cuda.empty_cache()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -287,10 +410,10 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-breakdown", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the extra.workloads record")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     w = parse_workload(args.workload)
@@ -312,61 +435,29 @@ def main():
         raise SystemExit("bench.py needs a CUDA GPU (there is no CPU path in this library)")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=device)
-        barrier = lambda: dist.barrier()
-    else:
-        dist = None
-        barrier = lambda: None
+    d = Dist(device)
+    world = d.world
 
     try:
         fns = get_impl(args.impl)
     except Exception as e:  # reference arm only: the package could not be imported
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}))
+        d.close()
         return
 
     # strong-scaling workloads shard their (batch, head) units; the default workload is weak
-    strong = bool(w.get("strong")) and world > 1
-    if strong:
-        from triton_sigmoid_b200.launcher import plan_shard, take_shard
-
-        sh = plan_shard(w["B"], w["H"], world, rank)
-        q, k, v, do, lens = make_data(w, device, 0)
-        q, k, v, do = [take_shard(t, sh).contiguous() for t in (q, k, v, do)]
-        wl = dict(w, B=sh.b1 - sh.b0, H=sh.h1 - sh.h0)
-    else:
-        q, k, v, do, lens = make_data(w, device, rank)
-        wl = w
+    wl, strong, q, k, v, do, lens = setup_workload(w, device, d)
     F = fwd_flops(wl, lens)
-    for t in (q, k, v):
-        t.requires_grad_()
     fwd_only, fwd_bwd = make_step(wl, fns, q, k, v, do, lens)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # > 126 MB L2
-
-    def reduce_max(x: float) -> float:
-        if dist is None:
-            return x
-        t = torch.tensor([x], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def reduce_sum(x: float) -> float:
-        if dist is None:
-            return x
-        t = torch.tensor([x], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
-
-    F_total = reduce_sum(F)
+    F_total = d.sum(F)
 
     # ---- headline: forward+backward, device-resident
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms_total = reduce_max(timed(fwd_bwd, args.steps, args.warmup, flush, barrier))
+    ms_total = d.max(timed(fwd_bwd, args.steps, args.warmup, flush, d.barrier))
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
     value = 3.5 * F_total / (ms_step * 1e-3) / 1e12
@@ -374,13 +465,16 @@ def main():
     # ---- end to end with host buffers
     e2e_fn, bi, bo = e2e_step_factory(wl, fns, q, k, v, do, lens)
     e2e_steps = max(3, min(args.steps, 10))
-    ms_e2e = reduce_max(timed(e2e_fn, e2e_steps, 3, flush, barrier)) / e2e_steps
+    ms_e2e = d.max(timed(e2e_fn, e2e_steps, 3, flush, d.barrier)) / e2e_steps
     e2e = {"value": 3.5 * F_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": bi,
-           "d2h_bytes_per_step": bo, "ms_per_step": ms_e2e}
+           "d2h_bytes_per_step": bo, "ms_per_step": ms_e2e,
+           "how": "pinned host tensors; per batch element H2D, forward+backward, D2H on three streams",
+           # what the host link alone allows: both directions at once, nothing else in the step
+           "pcie_bound_ms_at_50GBs": max(bi, bo) / 50e9 * 1e3}
 
     breakdown = {}
     if not args.no_breakdown:
-        ms_f = reduce_max(timed(fwd_only, args.steps, 3, flush, barrier)) / args.steps
+        ms_f = d.max(timed(fwd_only, args.steps, 3, flush, d.barrier)) / args.steps
         breakdown["fwd_tflops"] = F_total / (ms_f * 1e-3) / 1e12
         breakdown["fwd_ms"] = ms_f
         breakdown["fwd_bwd_tflops"] = value
@@ -396,7 +490,8 @@ def main():
         "config": {"workload": w["name"], "B_per_gpu": wl["B"], "N": w["N"], "H": wl["H"], "D": w["D"],
                    "causal": w["causal"], "padded": w["padded"], "global_batch": w["B"] if strong else w["B"] * world,
                    "parallelism": f"independent (batch, head) shards x{world}, no collective",
-                   "l2": "256 MiB buffer zero-filled between timed steps (L2 flush)", "impl": fns[2]},
+                   "l2": "256 MiB buffer zero-filled between timed steps (L2 flush)"},
+        "library": fns[2],
         "clocks": clocks, "e2e": e2e, "breakdown": breakdown,
         "peak_tflops": {"value": pk["burst"], "source": pk["source"]},
     }
@@ -409,13 +504,10 @@ def main():
         time_main_kernel("bwd", qd, kd, vd, do, **dict(kw, iters=3))
         kb = statistics.mean(time_main_kernel("bwd", qd, kd, vd, do, **kw))
         kf = statistics.mean(time_main_kernel("fwd", qd, kd, vd, **kw))
-        # DRAM bytes per (batch, token, head, d) element of one launch, from an ncu capture of a
-        # B=2 case of this workload (profiles/ncu_full_fwd_bwd_fp16_N4096_D64.md: backward 100.8 MB
-        # read + 22.9 MB written, forward 51.6 + 0.8 MB, for 2*4096*16*64 elements); DRAM traffic grows
-        # in proportion to the element count, so it is scaled to this launch.
         elems = float(wl["B"]) * w["N"] * wl["H"] * w["D"]
-        traffic_bwd = 14.74 * elems if (w["D"] == 64 and not w["padded"]) else None
-        traffic_fwd = 6.25 * elems if (w["D"] == 64 and not w["padded"]) else None
+        default_launch = w["name"] == "cfg2" and world == 1
+        traffic_bwd = NCU_DRAM_BYTES_DEFAULT_WORKLOAD["sigattn_bwd_kernel"] if default_launch else None
+        traffic_fwd = NCU_DRAM_BYTES_DEFAULT_WORKLOAD["sigattn_fwd_kernel"] if default_launch else None
         ach = 2.5 * F / (kb * 1e-3) / 1e12
         line["roofline"] = {"bound": "tensor", "kernel": "sigattn_bwd_kernel", "achieved": ach, "peak": pk["burst"],
                             "unit": "TFLOP/s", "frac": ach / pk["burst"], "traffic": traffic_bwd,
@@ -428,19 +520,35 @@ def main():
                             "hbm": {"bwd_gbs": 14.0 * elems / (kb * 1e-3) / 1e9, "fwd_gbs": 8.0 * elems / (kf * 1e-3) / 1e9,
                                     "peak_gbs": pk["hbm_gbs"], "bwd_frac": 14.0 * elems / (kb * 1e-3) / 1e9 / pk["hbm_gbs"],
                                     "fwd_frac": 8.0 * elems / (kf * 1e-3) / 1e9 / pk["hbm_gbs"]}}
+        # the other arm of the backward (two streaming kernels, no atomics), same launch, for the record
+        ks = statistics.mean(time_main_kernel("bwd", qd, kd, vd, do, **dict(kw, split_bwd=True)))
+        line["roofline"]["bwd_split_kernels"] = {"ms_per_launch_pair": ks, "achieved": 2.5 * F / (ks * 1e-3) / 1e12,
+                                                 "frac": 2.5 * F / (ks * 1e-3) / 1e12 / pk["burst"]}
         # kernels of this library per timed step: forward, backward, dQ convert
         line["gpu_launches"] = 3 * args.steps
-        if rank == 0 and world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(w)
     else:
         line["impl"] = "reference"
-        if rank == 0 and world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(w)
+
+    del q, k, v, do, fwd_only, fwd_bwd, e2e_fn
+    torch.cuda.empty_cache()
+    if not args.no_extra:
+        extra = {}
+        for name in EXTRA_WORKLOADS:
+            if name == w["name"]:
+                continue
+            try:
+                extra[name] = measure_extra(name, fns, device, d, flush, pk)
+            except Exception as e:  # a configuration that does not fit or fails is recorded, not fatal
+                extra[name] = {"error": f"{type(e).__name__}: {e}"[:200]}
+                torch.cuda.empty_cache()
+        line["extra"] = {"workloads": extra, "how": "3 warm-up + 3 timed steps each, CUDA events, L2 flushed between steps, max over ranks"}
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(w)
 
     if rank == 0:
         print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    d.close()
 
 
 if __name__ == "__main__":

@@ -12,13 +12,21 @@
  * Conventions
  *  - Every pointer in SigAttnParams is a DEVICE pointer owned by the caller.  The attention entry
  *    points allocate no device memory (only the diagnostic self-test does, 4 bytes for the duration
- *    of its call).  All launches are asynchronous on `stream`.
+ *    of its call); the library pins one 4 KB page of its own host data the first time it is used
+ *    (host-visible copies of the devices' health words, see sigattn_device_status).  All launches are
+ *    asynchronous on `stream`.  The first call on each device does a little set-up (symbol addresses,
+ *    kernel attributes): make it outside any stream capture.
  *  - Strides are in ELEMENTS; the head dimension is contiguous (stride 1).  Base pointers
  *    must be 16-byte aligned and every stride times the element size a multiple of 16 bytes.
  *  - The tensor-core kernels are persistent (one CTA per SM draws work items from a counter).  Each
- *    launch takes the next of 1024 counter pairs built into the library's device image and leaves it
- *    at zero when it ends (the pair is chosen on the host when the call is made), so up to 1024
- *    launches may be in flight per device at a time.
+ *    launch takes the next of a ring of counter pairs built into the library's device image and leaves
+ *    it at zero when it ends (the pair is chosen on the host when the call is made): 768 pairs serve
+ *    ordinary launches, so up to 768 of them may be in flight per device at a time; launches recorded
+ *    into a stream capture draw from 256 pairs of their own (a captured launch keeps its pair for every
+ *    replay), so a graph may hold up to 256 launches of this library and two graphs that share a pair
+ *    must not run at the same time.
+ *  - Return value -5: a kernel of this library gave up on a bounded wait on this device earlier; nothing
+ *    is launched until sigattn_device_status() has been called (which reports and clears the failure).
  *  - Return value 0 = launched; negative = rejected before any launch, with a message
  *    available from sigattn_last_error() on the calling thread.
  *  - Supported: dtype fp16 / bf16 / fp32, D in {64, 128}, 1 <= H, B, Tq, Tk (zero-sized problems
@@ -88,7 +96,7 @@ typedef struct SigAttnParams {
   const float *bias;         /* [B] fp32 additive bias, or NULL = bias_scalar */
   const float *score_mod;    /* [B,Tk] fp32 per-key additive bias (contiguous), or NULL */
 
-  void *workspace;           /* backward: >= sigattn_bwd_workspace_bytes(); forward: unused */
+  void *workspace;           /* backward: >= sigattn_bwd_workspace_bytes() (unused with SIGATTN_BWD_SPLIT); forward: unused */
   size_t workspace_bytes;
   void *stream;              /* cudaStream_t */
 
@@ -106,7 +114,9 @@ typedef struct SigAttnParams {
    * the number of sequences, Tq / Tk are upper bounds of the sequence lengths (longer sequences are cut
    * there), the batch strides are ignored, seq_lens_* must be NULL, score_mod is [total_k], the backward
    * workspace is sigattn_bwd_workspace_bytes(1, total_q, H, D) bytes (none for fp32), and only rows of
-   * the sequences are written. */
+   * the sequences are written: rows of q-side / k-side tensors that belong to no sequence (gaps, rows behind
+ * the last sequence, rows of a sequence beyond Tq / Tk) are left untouched in o, dq, dk, dv - pre-zero
+ * them if they are read afterwards. */
   const int32_t *cu_seqlens_q; /* [B+1] device, non-decreasing, cu_seqlens_q[B] <= total_q */
   const int32_t *cu_seqlens_k; /* [B+1] device */
   int32_t total_q, total_k;
@@ -123,7 +133,8 @@ int sigattn_fwd(const SigAttnParams *p);
  * sigmoid_attention_bwd_op + _bwd_dense_dq_kernel + _bwd_dense_dkdv_kernel
  * (sigmoid_triton_dense.py:162-467, 565-688) and the padded counterparts
  * (sigmoid_triton_padded.py:179-509, 626-772).  dQ rows >= seq_lens_q[b] and dK/dV rows
- * >= seq_lens_k[b] are written as zeros.  The fp32 dQ accumulator lives in `workspace`. */
+ * >= seq_lens_k[b] are written as zeros.  The default (fused) kernel keeps its fp32 dQ accumulator in
+ * `workspace`; with SIGATTN_BWD_SPLIT the two streaming kernels run instead and `workspace` is unused. */
 int sigattn_bwd(const SigAttnParams *p);
 
 /* Backward pass for callers that cannot hand the library a workspace.  (No counterpart in the
@@ -161,9 +172,9 @@ int sigattn_query(int what);
 /* Device-side health word of `device`: 0 = no kernel of this library has given up on a
  * bounded wait since the last call; otherwise a code identifying the wait (the results of
  * launches since the last call are then undefined; while the word is set further launches
- * do nothing).  Reading a non-zero word clears it and the kernels' work-item counters, so
- * the library can be used again.  Synchronises the device.  Negative = CUDA error (see
- * sigattn_last_error). */
+ * are refused with return value -5, and kernels already queued return at once).  Reading a non-zero
+ * word clears it and the kernels' work-item counters, so the library can be used again.  Synchronises
+ * the device.  Negative = CUDA error (see sigattn_last_error). */
 int sigattn_device_status(int device);
 
 /* Diagnostic (no counterpart in the reference): launches a one-warp kernel that waits, with a limit

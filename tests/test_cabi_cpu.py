@@ -88,3 +88,17 @@ def test_backward_needs_gradient_pointers(lib):
 def test_empty_batch_is_a_no_op(lib):
     assert lib.sigattn_fwd(ctypes.byref(_params(B=0))) == 0
     assert lib.sigattn_last_error() == b""
+
+
+def test_documented_reference_side_binding_is_runnable_python():
+    """The ctypes stub shown to the reference's maintainers imports and defines its op body
+    with the names this package really exports (executed up to, not including, a call)."""
+    import os
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "INTEGRATION.md")).read()
+    block = re.search(r"```python\n(.*?)```", text, re.S).group(1)
+    ns = {}
+    exec(compile(block, "INTEGRATION.md", "exec"), ns)
+    assert callable(ns["sigmoid_attention_fwd_op"]) and isinstance(ns["USE_ACCURATE_SIGMOID"], bool)

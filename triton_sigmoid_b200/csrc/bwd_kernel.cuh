@@ -29,13 +29,24 @@
 //                                  lanes cover a line, and adds them with red.global.add.v4.f32
 //                                  (the reduction traffic, not the math, is what bounds this case).
 //
-// Warp roles (20 warps):
+// Warp roles (20 warps; 28 at D = 64):
 //   warps 0-15  compute: warp w owns TMEM lanes (key rows) 32 (w & 3) .. +31 and the query
-//               columns 32 (w >> 2) .. +31 of every tile; the same warps drain dQ
+//               columns 32 (w >> 2) .. +31 of every tile; at D = 128 the same warps drain dQ
 //   warp  16    item scheduler + TMA producer (also clears padded rows of tiles that straddle a valid length)
 //   warp  17    tcgen05 issuer A: S^T and dP^T; owns the TMEM allocation
 //   warp  18    tcgen05 issuer B: dV, dK, dQ
 //   warp  19    idle
+//   warps 20-27 D = 64 only: dQ drain.  The reductions into the fp32 accumulator are slow to issue (the
+//               L2 serves a warp's reductions one 128-byte line at a time), and while the compute warps
+//               issued them themselves (29 % of their time, measured) the MUFU unit and the tensor pipe
+//               stood idle and the next tile's scores, which reuse the dQ columns, were late.  Eight
+//               warps that do nothing else take dQ out of TMEM as soon as it is complete (freeing the
+//               columns at once) and feed the reductions while the compute warps are two phases ahead.
+//               Registers are re-balanced with setmaxnreg (compute 80, role warps 72, drain warps 56 per thread);
+//               to fit, the compute warps do not keep P in registers between their two phases but read its
+//               16-bit copy back from TMEM.
+//               (No room for this at D = 128: the drain needs its whole tile in registers or shared
+//               memory before it can release the columns, and neither has any left there.)
 // Two issuing warps, because one warp's instruction stream (waits, 32 MMAs, commits per tile
 // pair) is a serial chain that otherwise bounds the kernel.  Everything the two exchange goes
 // through mbarriers: "S columns free" after dV, "dP columns free" after dK.
@@ -78,7 +89,9 @@ constexpr int kBwdComputeWarps = 16;
 constexpr int kBwdProducerWarp = 16;
 constexpr int kBwdIssuerA = 17;
 constexpr int kBwdIssuerB = 18;
-constexpr int kBwdThreads = 20 * 32;
+constexpr int kBwdDrainWarps = 8;    // D = 64 only
+constexpr int kBwdFirstDrainWarp = 20;
+template <int D> constexpr int kBwdThreads = (D == 64) ? (kBwdFirstDrainWarp + kBwdDrainWarps) * 32 : 20 * 32;
 constexpr int kBwdTileKV = 128;
 constexpr int kBwdTileQ = 128;
 
@@ -95,13 +108,13 @@ struct BwdSmem {
   static constexpr int kDoOff = kQOff + kStages * kTileBytes;
   static constexpr int kDsOff = kDoOff + kStages * kTileBytes;
   static constexpr int kDsBytes = 128 * 128 * 2;
-  // D = 64 only: a private patch of 16 rows x 128 bytes per compute warp, used to regroup dQ rows so
+  // D = 64 only: a private patch of 32 rows x 128 bytes per drain warp, used to regroup dQ rows so
   // that eight adjacent lanes add the 128 bytes of one row (16 bytes of padding per row keep the
   // 16-byte accesses of different rows off each other's banks)
   static constexpr int kDqPatchRow = 128 + 16;
   static constexpr int kDqPatchOff = kDsOff + kDsBytes;
-  static constexpr int kDqPatchBytes = (D == 64) ? 16 * kDqPatchRow : 0;
-  static constexpr int kBarOff = kDqPatchOff + 16 * kDqPatchBytes;
+  static constexpr int kDqPatchBytes = (D == 64) ? 32 * kDqPatchRow : 0;
+  static constexpr int kBarOff = kDqPatchOff + kBwdDrainWarps * kDqPatchBytes;
   static constexpr int kKvFull = 0;                   // [2] per K/V buffer
   static constexpr int kQFull = 2;                    // [2]
   static constexpr int kQEmpty = kQFull + kStages;    // [2]  both issuers release a stage
@@ -229,6 +242,96 @@ __device__ __forceinline__ void bwd_phase_b(uint32_t dp_addr, uint32_t ds_line, 
   }
 }
 
+// The two phases for the D = 64 kernel.  The probabilities are not kept in registers between the phases
+// (32 registers per thread that the drain warps' share of the register file cannot spare) but read back
+// from TMEM in the 16-bit form they were stored in for the dV product, and dS = P (1 - P) dP is formed on
+// packed 16-bit pairs.
+template <bool kBF16, bool kMask, bool kAccurate>
+__device__ __forceinline__ void bwd_phase_a16(uint32_t s_addr, float c1, float c0, int q0, int q_lo, int q_hi) {
+  uint32_t r[32];
+  tmem_ld32_sync(s_addr, r);
+  uint32_t pk[16];
+  float2 t[16];
+  const float c0s = (kMask || kAccurate) ? c0 : c0 + kDeepShift;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    t[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), make_float2(c1, c1),
+                      make_float2(c0s, c0s));
+  if constexpr (kAccurate) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float2 pe = sigmoid2_accurate_from_log2(t[i]);
+      if constexpr (kMask) {
+        const int q = q0 + 2 * i;
+        pe.x = (q >= q_lo && q < q_hi) ? pe.x : 0.0f;
+        pe.y = (q + 1 >= q_lo && q + 1 < q_hi) ? pe.y : 0.0f;
+      }
+      pk[i] = pack2<kBF16>(pe.x, pe.y);
+    }
+  } else if (!kMask && warp_all_negative(t)) {
+    // all logits far below zero (the usual case under the default bias): short series on packed pairs
+#pragma unroll
+    for (int i = 0; i < 16; ++i) pk[i] = sigmoid2_deep_packed<kBF16>(t[i], false);
+  } else {
+    bool all_neg = false;
+    if constexpr (!kMask) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) t[i] = __fadd2_rn(t[i], make_float2(-kDeepShift, -kDeepShift));
+      all_neg = warp_all_negative(t);
+    }
+    if (all_neg) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float2 pe = sigmoid2_from_log2_neg<kBF16>(t[i]);
+        pk[i] = pack2<kBF16>(pe.x, pe.y);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float2 pe = sigmoid2_from_log2<kBF16>(t[i]);
+        if constexpr (kMask) {
+          const int q = q0 + 2 * i;
+          pe.x = (q >= q_lo && q < q_hi) ? pe.x : 0.0f;
+          pe.y = (q + 1 >= q_lo && q + 1 < q_hi) ? pe.y : 0.0f;
+        }
+        pk[i] = pack2<kBF16>(pe.x, pe.y);
+      }
+    }
+  }
+  tmem_st16(s_addr, pk);
+}
+
+template <bool kBF16, bool kMask>
+__device__ __forceinline__ void bwd_phase_b16(uint32_t p_addr, uint32_t dp_addr, uint32_t ds_line, uint32_t chunk0,
+                                              uint32_t sw) {
+  uint32_t pp[16], r[32];
+  tmem_ld16(p_addr, pp);
+  tmem_ld32(dp_addr, r);
+  tmem_ld_wait_for(pp);
+  tmem_ld_wait_for(r);
+  uint32_t pk[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t ph = pp[i];
+    const uint32_t w = hfma2<kBF16>(ph ^ 0x80008000u, ph, ph);  // P - P^2
+    uint32_t d = hmul2<kBF16>(w, pack2<kBF16>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
+    if constexpr (kMask) {
+      // masked elements have P exactly 0: force dS to 0 there, whatever (NaN, Inf) the padding put into dP
+      const uint32_t keep = ((ph & 0x00007fffu) ? 0x0000ffffu : 0u) | ((ph & 0x7fff0000u) ? 0xffff0000u : 0u);
+      d &= keep;
+    }
+    pk[i] = d;
+  }
+  tmem_st16(dp_addr, pk);
+#pragma unroll
+  for (int m = 0; m < 4; ++m) {
+    const uint32_t chunk = (chunk0 + m) ^ sw;  // 128-byte swizzle: 16-byte chunk index XOR (row & 7)
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ds_line + chunk * 16), "r"(pk[4 * m]),
+                 "r"(pk[4 * m + 1]), "r"(pk[4 * m + 2]), "r"(pk[4 * m + 3])
+                 : "memory");
+  }
+}
+
 // One work item, decoded the same way by every warp role.
 struct BwdItem {
   int b, h, kv0;
@@ -281,7 +384,7 @@ __device__ __forceinline__ BwdItem bwd_decode_item(const BwdParams& p, int item)
 }
 
 template <int D, bool kBF16, bool kAccurate>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads<D>, 1)
 sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                    const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap do_map,
                    const BwdParams p) {
@@ -308,7 +411,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   // where dQ (or dQ^T) of tile g is written
   auto dq_col = [&](int g) -> uint32_t { return kTwoS ? kColS + 128u * (uint32_t)(g & 1) : kColDp; };
   constexpr int kSiteBase = 0x20000;
-  constexpr int kItemReaders = kBwdComputeWarps + 2;  // compute warps and the two issuing warps
+  constexpr bool kDrainWarps = kTwoS;  // dedicated dQ drain warps (see the file header)
+  // compute warps, the two issuing warps and the drain warps read the item ring
+  constexpr int kItemReaders = kBwdComputeWarps + 2 + (kDrainWarps ? kBwdDrainWarps : 0);
 
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -350,8 +455,8 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     mbar_init(bar(L::kDpFree), 1);
     mbar_init(bar(L::kDqFull + 0), 1);
     mbar_init(bar(L::kDqFull + 1), 1);
-    mbar_init(bar(L::kDqEmpty + 0), kBwdComputeWarps);
-    mbar_init(bar(L::kDqEmpty + 1), kBwdComputeWarps);
+    mbar_init(bar(L::kDqEmpty + 0), kDrainWarps ? kBwdDrainWarps : kBwdComputeWarps);
+    mbar_init(bar(L::kDqEmpty + 1), kDrainWarps ? kBwdDrainWarps : kBwdComputeWarps);
     mbar_init(bar(L::kDkvFull), 1);
     mbar_init(bar(L::kDkvEmpty), kBwdComputeWarps);
     for (int i = 0; i < 2; ++i) {
@@ -386,6 +491,70 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     return item;
   };
 
+  if constexpr (kDrainWarps) {
+    // 896 threads get 72 registers each at launch.  Each aligned group of four warps executes one
+    // instruction; the counts add up to exactly what the CTA holds (512 x 80 + 128 x 72 + 256 x 56).
+    // (The issuing warps are the ones that must not spill: their instruction stream is the critical chain.)
+    if (warp < kBwdComputeWarps)         setmaxnreg_inc<80>();
+    else if (warp >= kBwdFirstDrainWarp) setmaxnreg_dec<56>();
+  }
+
+  if (kDrainWarps && warp >= kBwdFirstDrainWarp) {
+    // ============================================================ dQ drain (D = 64)
+    // Warp d = warp - 20: lane quarter d & 3 (32 query rows), head columns [32 (d >> 2), +32) = one 128-byte
+    // line of the accumulator per row.  Per tile: wait for the dQ product, move the 32 x 32 block through
+    // registers into the warp's shared-memory patch, release the TMEM columns, then add the rows into the
+    // accumulator with red.global.add.v4.f32, eight adjacent lanes per line.
+    if constexpr (kDrainWarps) {
+      const int dw = warp - kBwdFirstDrainWarp;
+      const int quarter = dw & 3, half = dw >> 2;
+      const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+      uint8_t* patch = smem_gen + L::kDqPatchOff + dw * L::kDqPatchBytes;
+      int g = 0;
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        const int item = read_item(k);
+        if (item < 0) break;
+        const BwdItem it = bwd_decode_item(p, item);
+        if (it.n_q == 0) continue;
+        for (int t = 0; t < it.n_q && ok; ++t) {
+          const int gt = g + t;
+          ok = mbar_wait_warp(bar(L::kDqFull + sbuf(gt)), spar(gt), abort_flag, kSiteBase + 14);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t addr = tmem + lane_addr + dq_col(gt) + 32u * (uint32_t)half;
+          uint4* mine = reinterpret_cast<uint4*>(patch + lane * L::kDqPatchRow);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            uint32_t r[16];
+            tmem_ld(addr + 16 * u, r);
+            tmem_ld_wait_for(r);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) mine[4 * u + m] = make_uint4(r[4 * m], r[4 * m + 1], r[4 * m + 2], r[4 * m + 3]);
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(gt)));  // the TMEM columns are free again
+          const int q_tile = (it.i_begin + t) * kBwdTileQ + quarter * 32;
+          const int slot = lane >> 3, chunk = lane & 7;  // patch row within a group of four, 16-byte chunk of the row
+#pragma unroll
+          for (int kq = 0; kq < 8; ++kq) {
+            const int prow = 4 * kq + slot;
+            const int q = q_tile + prow;
+            const uint4 w = *reinterpret_cast<const uint4*>(patch + prow * L::kDqPatchRow + chunk * 16);
+            if (q < it.Lq) {  // queries at or beyond Lq get no gradient
+              float* dst = p.dq_acc + ((it.acc_row0 + q) * p.H + it.h) * D + 32 * half + 4 * chunk;
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(w.x)),
+                           "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
+                           : "memory");
+            }
+          }
+          __syncwarp();  // the patch is rewritten at the next tile
+        }
+        g += it.n_q;
+      }
+    }
+  } else
   if (warp == kBwdProducerWarp) {
     // ============================================================ item scheduler + TMA producer
     // Rows beyond the valid lengths may hold anything (NaN included).  Masked probabilities are
@@ -607,25 +776,32 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         ok = mbar_wait_warp(bar(L::kDsReady), par, abort_flag, kSiteBase + 9);
         if (!ok) break;
         tc_fence_after_sync();
+        if constexpr (kTwoS) {
+          // dQ first: the group that owns the tile waits for it before it can move on
+#pragma unroll
+          for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
+            const uint64_t kd = make_desc(k_lo + kv_off + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
+            mma_ss(leader, tmem + dq_col(gt), dsd, kd, idesc_dq, kk > 0);
+          }
+          mma_commit(leader, bar(L::kDqFull + sbuf(gt)));
+        }
         issue_acc(kColDk, kColDp, q_lo0 + (uint32_t)st * kStageStep, acc0);
         if (!kDqT) mma_commit(leader, bar(L::kDpFree));
         mma_commit(leader, bar(L::kQEmpty + st));
         // dK_j, dV_j are complete with the last tile's dK: the epilogue need not wait for its dQ
         if (t == it.n_q - 1) mma_commit(leader, bar(L::kDkvFull));
-        // the dQ GEMM needs the previous dQ tile read out of its columns
         if constexpr (!kTwoS) {
+          // the dQ GEMM needs the previous dQ tile read out of its columns
           ok = mbar_wait_warp(bar(L::kDqEmpty), par ^ 1u, abort_flag, kSiteBase + 10);
           if (!ok) break;
           tc_fence_after_sync();
-        }
-        // (two S buffers: dQ goes over this tile's own S^T buffer; dV above, issued by this same
-        //  thread and therefore executed earlier, was the last reader of P^T in it)
 #pragma unroll
-        for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
-          const uint64_t kd = make_desc(k_lo + kv_off + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
-          mma_ss(leader, tmem + dq_col(gt), kDqT ? kd : dsd, kDqT ? dsd : kd, idesc_dq, kk > 0);
+          for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
+            const uint64_t kd = make_desc(k_lo + kv_off + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
+            mma_ss(leader, tmem + dq_col(gt), kDqT ? kd : dsd, kDqT ? dsd : kd, idesc_dq, kk > 0);
+          }
+          mma_commit(leader, bar(L::kDqFull + sbuf(gt)));
         }
-        mma_commit(leader, bar(L::kDqFull + sbuf(gt)));
       }
       if (!ok) break;
       mma_commit(leader, bar(L::kKvEmpty + kb));  // the dQ products were this warp's readers of K_j
@@ -682,6 +858,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const bool row_ok = kv < Lk;
 
       // ---- dQ drain (see the file header); t = index within the item of the query tile whose dQ is complete
+      // ---- dQ^T drain by the compute warps themselves (D = 128; at D = 64 the drain warps do it): lane l of
+      // quarter k holds d = 32 k + l, this warp takes query columns 32 cg ..; one red.global.add.f32 per
+      // query covers a full 128-byte line.  t = index within the item of the query tile whose dQ is complete
       auto drain_dq = [&](int t) {
         const int gt = g + t;
         ok = mbar_wait_warp(bar(L::kDqFull + sbuf(gt)), spar(gt), abort_flag, kSiteBase + 14);
@@ -689,56 +868,19 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         if (!ok) return;
         tc_fence_after_sync();
         const int q_tile = (i_begin + t) * kBwdTileQ;
-        if constexpr (kDqT) {
-          uint32_t r[32];
-          tmem_ld32_sync(dq_addr, r);
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(gt)));  // the TMEM columns are free again
-          const int q_first = q_tile + 32 * cg;
-          float* dst = p.dq_acc + ((it.acc_row0 + q_first) * p.H + h) * D + lane_row;
-          const int64_t row_stride = (int64_t)p.H * D;
-          const int n_live = min(32, Lq - q_first);  // queries at or beyond Lq get no gradient
+        uint32_t r[32];
+        tmem_ld32_sync(dq_addr, r);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(gt)));  // the TMEM columns are free again
+        const int q_first = q_tile + 32 * cg;
+        float* dst = p.dq_acc + ((it.acc_row0 + q_first) * p.H + h) * D + lane_row;
+        const int64_t row_stride = (int64_t)p.H * D;
+        const int n_live = min(32, Lq - q_first);  // queries at or beyond Lq get no gradient
 #pragma unroll
-          for (int v = 0; v < 32; ++v) {
-            if (v < n_live)
-              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + v * row_stride), "f"(__uint_as_float(r[v])) : "memory");
-          }
-        } else {
-          // A warp's reduction instructions are served one 128-byte line at a time (~17 clocks each), so
-          // the number of lines a warp touches is what its stall costs.  This warp therefore takes half
-          // of the head dimension (32 columns = one full line per row) of every second row of its lane
-          // quarter: 16 lines per tile, the minimum for 16 warps.  The rows are regrouped through the
-          // warp's shared-memory patch so that eight adjacent lanes cover the 128 bytes of one row.
-          // (Tried and slower: 64-byte runs of all 32 rows; bulk reductions out of shared memory, which
-          // compete with the tile loads for the copy engine; a separate reduction warp, which serialises.)
-          const int col_half = cg & 1, row_par = cg >> 1;
-          uint32_t r[32];
-          tmem_ld32_sync(dq_off - 16 * cg + dq_col(gt) + 32 * col_half, r);
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(L::kDqEmpty + sbuf(gt)));
-          uint8_t* patch = smem_gen + L::kDqPatchOff + warp * L::kDqPatchBytes;
-          if ((lane & 1) == row_par) {
-            uint4* mine = reinterpret_cast<uint4*>(patch + (lane >> 1) * L::kDqPatchRow);
-#pragma unroll
-            for (int m = 0; m < 8; ++m) mine[m] = make_uint4(r[4 * m], r[4 * m + 1], r[4 * m + 2], r[4 * m + 3]);
-          }
-          __syncwarp();
-          const int slot = lane >> 3, chunk = lane & 7;  // patch row slot (within a group of four) and 16-byte chunk
-#pragma unroll
-          for (int kq = 0; kq < 4; ++kq) {
-            const int prow = 4 * kq + slot;                                  // patch row = (row within quarter) / 2
-            const int q = q_tile + quarter * 32 + 2 * prow + row_par;
-            const uint4 w = *reinterpret_cast<const uint4*>(patch + prow * L::kDqPatchRow + chunk * 16);
-            if (q < Lq) {  // queries at or beyond Lq get no gradient
-              float* dst = p.dq_acc + ((it.acc_row0 + q) * p.H + h) * D + 32 * col_half + 4 * chunk;
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(w.x)),
-                           "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
-                           : "memory");
-            }
-          }
-          __syncwarp();  // the patch is rewritten at the next tile
+        for (int v = 0; v < 32; ++v) {
+          if (v < n_live)
+            asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + v * row_stride), "f"(__uint_as_float(r[v])) : "memory");
         }
       };
 
@@ -755,16 +897,26 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         const uint32_t s_addr = s_addr0 + 128u * (uint32_t)sbuf(gt);
         if (!ok) break;
         tc_fence_after_sync();
-        if (need_mask) bwd_phase_a<kBF16, true, kAccurate>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
-        else           bwd_phase_a<kBF16, false, kAccurate>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
+        if constexpr (kDrainWarps) {
+          if (need_mask) bwd_phase_a16<kBF16, true, kAccurate>(s_addr, c1, c0, q0, q_lo, q_hi);
+          else           bwd_phase_a16<kBF16, false, kAccurate>(s_addr, c1, c0, q0, q_lo, q_hi);
+        } else {
+          if (need_mask) bwd_phase_a<kBF16, true, kAccurate>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
+          else           bwd_phase_a<kBF16, false, kAccurate>(s_addr, c1, c0, q0, q_lo, q_hi, pv);
+        }
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kPReady + sbuf(gt)));
 
-        // dQ of the previous tile is complete by now (or soon): drain it while dP^T is computed.
-        // Its completion also means the dQ GEMM no longer reads the shared-memory copy of dS.
-        if (t > 0) {
+        if constexpr (kDrainWarps) {
+          // the dQ product of the previous tile (of this or the previous item) reads the shared-memory copy
+          // of dS until it is complete; phase B below rewrites that copy
+          if (gt > 0) ok = mbar_wait_warp(bar(L::kDqFull + sbuf(gt - 1)), spar(gt - 1), abort_flag, kSiteBase + 16);
+          if (!ok) break;
+        } else if (t > 0) {
+          // dQ of the previous tile is complete by now (or soon): drain it while dP^T is computed.
+          // Its completion also means the dQ GEMM no longer reads the shared-memory copy of dS.
           drain_dq(t - 1);
           if (!ok) break;
         }
@@ -772,8 +924,13 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         ok = mbar_wait_warp(bar(L::kDpFull), (uint32_t)gt & 1u, abort_flag, kSiteBase + 13);
         if (!ok) break;
         tc_fence_after_sync();
-        if (need_mask) bwd_phase_b<kBF16, true>(dp_addr, ds_line, chunk0, sw, pv);
-        else           bwd_phase_b<kBF16, false>(dp_addr, ds_line, chunk0, sw, pv);
+        if constexpr (kDrainWarps) {
+          if (need_mask) bwd_phase_b16<kBF16, true>(s_addr, dp_addr, ds_line, chunk0, sw);
+          else           bwd_phase_b16<kBF16, false>(s_addr, dp_addr, ds_line, chunk0, sw);
+        } else {
+          if (need_mask) bwd_phase_b<kBF16, true>(dp_addr, ds_line, chunk0, sw, pv);
+          else           bwd_phase_b<kBF16, false>(dp_addr, ds_line, chunk0, sw, pv);
+        }
         fence_proxy_async_smem();
         tmem_st_wait();
         tc_fence_before_sync();
@@ -821,8 +978,10 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           }
         }
       }
-      drain_dq(n_q - 1);
-      if (!ok) break;
+      if constexpr (!kDrainWarps) {
+        drain_dq(n_q - 1);
+        if (!ok) break;
+      }
       g += n_q;
       ++act;
     }

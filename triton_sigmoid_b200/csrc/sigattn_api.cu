@@ -363,7 +363,7 @@ int launch_bwd_fused(const SigAttnParams* p, const CUtensorMap& qm, const CUtens
     // persistent: one CTA per SM (the kernel's shared memory allows no more), fewer when there are fewer items
     dim3 grid((unsigned int)std::min<int64_t>(n_items, info.n_sm));
     if (p->ev_main_start) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream));
-    kernel<<<grid, kBwdThreads, smem, stream>>>(qm, km, vm, dom, bp);
+    kernel<<<grid, kBwdThreads<D>, smem, stream>>>(qm, km, vm, dom, bp);
     SIG_CUDA(cudaGetLastError());
     if (p->ev_main_stop) SIG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_stop), stream));
   }
