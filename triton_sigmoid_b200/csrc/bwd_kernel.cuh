@@ -136,8 +136,8 @@ struct BwdSmem {
   static constexpr int kItemFull = kDkvEmpty + 1;     // [2] item index published
   static constexpr int kItemEmpty = kItemFull + 2;    // [2] item index read by every consumer warp
   static constexpr int kNumBars = kItemEmpty + 2;
-  static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int), item ring (2 int)
-  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int), 2 x item record (16 int each)
+  static constexpr int kTotal = kMiscOff + 16 + 2 * 64;
   static constexpr int kDynBytes = kTotal + 1024;
 };
 
@@ -332,7 +332,8 @@ __device__ __forceinline__ void bwd_phase_b16(uint32_t p_addr, uint32_t dp_addr,
   }
 }
 
-// One work item, decoded the same way by every warp role.
+// One work item.  The producer warp decodes it once (integer divisions, length and bias loads from global
+// memory) and publishes the record through shared memory; every other role reads it from there.
 struct BwdItem {
   int b, h, kv0;
   int bc;               // batch coordinate of the tensor maps and strides (0 when packed)
@@ -343,7 +344,25 @@ struct BwdItem {
   int i_begin, n_q;     // first query tile that sees this key tile, number of query tiles
   bool ragged_kv;       // the key tile straddles Lk
   bool ragged_last_q;   // the last query tile straddles Lq
+  float bias;           // additive bias of the item's batch element
 };
+// record layout in shared memory: 16 ints, [0] = item index (-1: no more work)
+__device__ __forceinline__ void bwd_publish_item(volatile int* rec, int item, const BwdItem& it) {
+  rec[1] = it.b; rec[2] = it.h; rec[3] = it.kv0; rec[4] = it.bc; rec[5] = it.tq0; rec[6] = it.tk0; rec[7] = it.key_lim;
+  rec[8] = (int)(uint32_t)((uint64_t)it.acc_row0 & 0xffffffffull); rec[9] = (int)(uint32_t)((uint64_t)it.acc_row0 >> 32);
+  rec[10] = it.Lq; rec[11] = it.Lk; rec[12] = it.i_begin; rec[13] = it.n_q;
+  rec[14] = (it.ragged_kv ? 1 : 0) | (it.ragged_last_q ? 2 : 0); rec[15] = __float_as_int(it.bias);
+  rec[0] = item;
+}
+__device__ __forceinline__ BwdItem bwd_load_item(const volatile int* rec) {
+  BwdItem it;
+  it.b = rec[1]; it.h = rec[2]; it.kv0 = rec[3]; it.bc = rec[4]; it.tq0 = rec[5]; it.tk0 = rec[6]; it.key_lim = rec[7];
+  it.acc_row0 = (int64_t)(((uint64_t)(uint32_t)rec[9] << 32) | (uint64_t)(uint32_t)rec[8]);
+  it.Lq = rec[10]; it.Lk = rec[11]; it.i_begin = rec[12]; it.n_q = rec[13];
+  const int fl = rec[14];
+  it.ragged_kv = (fl & 1) != 0; it.ragged_last_q = (fl & 2) != 0; it.bias = __int_as_float(rec[15]);
+  return it;
+}
 __device__ __forceinline__ BwdItem bwd_decode_item(const BwdParams& p, int item) {
   BwdItem it;
   // Groups of `group` (batch, head) pairs: within a group every pair's key tile 0 comes first, then
@@ -380,6 +399,7 @@ __device__ __forceinline__ BwdItem bwd_decode_item(const BwdParams& p, int item)
   it.n_q = (it.kv0 < it.Lk) ? max(i_end - it.i_begin, 0) : 0;
   it.ragged_kv = it.kv0 + kBwdTileKV > it.Lk;
   it.ragged_last_q = (it.i_begin + it.n_q) * kBwdTileQ > it.Lq;  // only the last query tile can straddle Lq
+  it.bias = p.bias ? p.bias[it.b] : p.bias_scalar;
   return it;
 }
 
@@ -422,7 +442,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   auto bar = [&](int slot) -> uint32_t { return bars + 8u * slot; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
-  volatile int* item_ring = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 8);  // [2]
+  volatile int* item_ring = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 16);  // 2 records of 16 ints
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -482,10 +502,11 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
 
   // Consumer side of the item ring: returns the k-th item of this CTA, or -1 when there is none
   // (also on a failed wait).  Called by all 32 lanes of a reader warp.
-  auto read_item = [&](int k) -> int {
+  auto read_item = [&](int k, BwdItem& it) -> int {
     const int slot = k & 1;
     if (!mbar_wait_warp(bar(L::kItemFull + slot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30)) return -1;
-    const int item = item_ring[slot];
+    const int item = item_ring[16 * slot];
+    if (item >= 0) it = bwd_load_item(item_ring + 16 * slot);
     __syncwarp();
     if (lane == 0) mbar_arrive(bar(L::kItemEmpty + slot));
     return item;
@@ -513,9 +534,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       int g = 0;
       bool ok = true;
       for (int k = 0; ok; ++k) {
-        const int item = read_item(k);
+        BwdItem it;
+        const int item = read_item(k, it);
         if (item < 0) break;
-        const BwdItem it = bwd_decode_item(p, item);
         if (it.n_q == 0) continue;
         for (int t = 0; t < it.n_q && ok; ++t) {
           const int gt = g + t;
@@ -577,17 +598,19 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       ok = mbar_wait_warp(bar(L::kItemEmpty + slot), ((uint32_t)(k >> 1) & 1u) ^ 1u, abort_flag, kSiteBase + 31);
       if (!ok) break;
       int item = blockIdx.x;  // the first item needs no ticket
-      if (lane == 0) {
-        if (k > 0) {
-          const unsigned int tk = atomicAdd(p.ticket, 1u) + gridDim.x;
-          item = tk < (unsigned int)p.n_items ? (int)tk : -1;
-        }
-        item_ring[slot] = item;
-        mbar_arrive(bar(L::kItemFull + slot));
+      if (lane == 0 && k > 0) {
+        const unsigned int tk = atomicAdd(p.ticket, 1u) + gridDim.x;
+        item = tk < (unsigned int)p.n_items ? (int)tk : -1;
       }
       item = __shfl_sync(0xffffffffu, item, 0);
+      BwdItem it = {};
+      if (item >= 0) it = bwd_decode_item(p, item);
+      if (lane == 0) {
+        if (item >= 0) bwd_publish_item(item_ring + 16 * slot, item, it);
+        else item_ring[16 * slot] = -1;
+        mbar_arrive(bar(L::kItemFull + slot));  // (release: the record is visible to whoever sees the phase)
+      }
       if (item < 0) break;
-      const BwdItem it = bwd_decode_item(p, item);
       if (it.n_q == 0) continue;
 
       for (int t = 0; t < it.n_q && ok; ++t) {
@@ -675,9 +698,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     uint32_t qfix_par = 0u;   // bit st: parity of stage st's "padded Q / dO rows cleared"
     bool ok = true;
     for (int k = 0; ok; ++k) {
-      const int item = read_item(k);
+      BwdItem it;
+      const int item = read_item(k, it);
       if (item < 0) break;
-      const BwdItem it = bwd_decode_item(p, item);
       if (it.n_q == 0) continue;
       const int kb = act % L::kKvBufs;
       const uint32_t kv_off = (uint32_t)kb * kStageStep;  // this item's K_j / V_j buffer, in descriptor address units
@@ -752,9 +775,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     int act = 0;  // items with work so far
     bool ok = true;
     for (int k = 0; ok; ++k) {
-      const int item = read_item(k);
+      BwdItem it;
+      const int item = read_item(k, it);
       if (item < 0) break;
-      const BwdItem it = bwd_decode_item(p, item);
       if (it.n_q == 0) continue;
       const int kb = act % L::kKvBufs;
       const uint32_t kv_off = (uint32_t)kb * kStageStep;
@@ -830,9 +853,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     bool ok = true;
 
     for (int k = 0; ok; ++k) {
-      const int item = read_item(k);
+      BwdItem it;
+      const int item = read_item(k, it);
       if (item < 0) break;
-      const BwdItem it = bwd_decode_item(p, item);
       const int b = it.b, h = it.h, kv0 = it.kv0, Lq = it.Lq, Lk = it.Lk, i_begin = it.i_begin, n_q = it.n_q;
       const int kv = kv0 + lane_row;
       // row 0 of this sequence's dK / dV
@@ -852,7 +875,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         }
         continue;
       }
-      float c0 = p.bias ? p.bias[b] : p.bias_scalar;
+      float c0 = it.bias;
       if (p.score_mod && kv < it.key_lim) c0 += p.score_mod[(p.cu_k ? (int64_t)it.tk0 : (int64_t)b * p.Tk) + kv];
       c0 *= kLog2e;
       const bool row_ok = kv < Lk;

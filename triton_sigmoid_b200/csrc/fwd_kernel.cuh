@@ -102,8 +102,8 @@ struct FwdSmem {
   static constexpr int kItemFull = kOEmpty + 1;       // [2] item index published
   static constexpr int kItemEmpty = kItemFull + 2;    // [2] item index read by every consumer warp
   static constexpr int kNumBars = kItemEmpty + 2;
-  static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int), item ring (2 int)
-  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int), 2 x item record (16 int each)
+  static constexpr int kTotal = kMiscOff + 16 + 2 * 64;
   static constexpr int kDynBytes = kTotal + 1024;  // slack to align the base to 1024 bytes
 };
 
@@ -233,7 +233,9 @@ __device__ __forceinline__ void fwd_sigmoid_chunk(uint32_t s_addr, const uint32_
   fwd_chunk_probs<kBF16, kMask, kAccurate>(s_addr, t, col0, lim);
 }
 
-// One work item, decoded the same way by every warp role.
+// One work item.  The producer warp decodes it once (integer divisions, length and bias loads from global
+// memory) and publishes the record through shared memory; every other role reads it from there - decoding
+// in each of the eighteen consumer warps cost the sigmoid warps about two thousand clocks per item.
 struct FwdItem {
   int b, h, q0;
   int bc;             // batch coordinate of the tensor maps and strides (0 when packed)
@@ -242,7 +244,22 @@ struct FwdItem {
   int key_lim;        // keys below this have a score_mod entry (Tk; packed: Lk)
   int Lq, Lk;
   int n0, n1, n_max;  // key tiles of query tile 0 / 1, and the larger of the two
+  float bias;         // additive bias of the item's batch element
 };
+// record layout in shared memory: 16 ints, [0] = item index (-1: no more work)
+__device__ __forceinline__ void fwd_publish_item(volatile int* rec, int item, const FwdItem& it) {
+  rec[1] = it.b; rec[2] = it.h; rec[3] = it.q0; rec[4] = it.bc; rec[5] = it.tq0; rec[6] = it.tk0;
+  rec[7] = it.row_lim; rec[8] = it.key_lim; rec[9] = it.Lq; rec[10] = it.Lk; rec[11] = it.n0; rec[12] = it.n1;
+  rec[13] = it.n_max; rec[14] = __float_as_int(it.bias);
+  rec[0] = item;
+}
+__device__ __forceinline__ FwdItem fwd_load_item(const volatile int* rec) {
+  FwdItem it;
+  it.b = rec[1]; it.h = rec[2]; it.q0 = rec[3]; it.bc = rec[4]; it.tq0 = rec[5]; it.tk0 = rec[6];
+  it.row_lim = rec[7]; it.key_lim = rec[8]; it.Lq = rec[9]; it.Lk = rec[10]; it.n0 = rec[11]; it.n1 = rec[12];
+  it.n_max = rec[13]; it.bias = __int_as_float(rec[14]);
+  return it;
+}
 __device__ __forceinline__ FwdItem fwd_decode_item(const FwdParams& p, int item) {
   FwdItem it;
   // Items are ordered in groups of `group` (batch, head) pairs: within a group all pairs' heaviest
@@ -287,6 +304,7 @@ __device__ __forceinline__ FwdItem fwd_decode_item(const FwdParams& p, int item)
   it.n0 = n_kv[0];
   it.n1 = n_kv[1];
   it.n_max = max(it.n0, it.n1);
+  it.bias = p.bias ? p.bias[it.b] : p.bias_scalar;
   return it;
 }
 
@@ -317,7 +335,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   auto bar = [&](int slot) -> uint32_t { return bars + 8u * slot; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
-  volatile int* item_ring = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 8);  // [2]
+  volatile int* item_ring = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 16);  // 2 records of 16 ints
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -371,10 +389,11 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
 
   // Consumer side of the item ring: returns the k-th item of this CTA, or -1 when there is none
   // (also on a failed wait).  Called by all 32 lanes of a reader warp.
-  auto read_item = [&](int k) -> int {
+  auto read_item = [&](int k, FwdItem& it) -> int {
     const int slot = k & 1;
     if (!mbar_wait_warp(bar(L::kItemFull + slot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30)) return -1;
-    const int item = item_ring[slot];
+    const int item = item_ring[16 * slot];
+    if (item >= 0) it = fwd_load_item(item_ring + 16 * slot);
     __syncwarp();
     if (lane == 0) mbar_arrive(bar(L::kItemEmpty + slot));
     return item;
@@ -394,17 +413,19 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       ok = mbar_wait_warp(bar(L::kItemEmpty + slot), ((uint32_t)(k >> 1) & 1u) ^ 1u, abort_flag, kSiteBase + 31);
       if (!ok) break;
       int item = blockIdx.x;  // the first item needs no ticket
-      if (lane == 0) {
-        if (k > 0) {
-          const unsigned int t = atomicAdd(p.ticket, 1u) + gridDim.x;
-          item = t < (unsigned int)p.n_items ? (int)t : -1;
-        }
-        item_ring[slot] = item;
-        mbar_arrive(bar(L::kItemFull + slot));
+      if (lane == 0 && k > 0) {
+        const unsigned int t = atomicAdd(p.ticket, 1u) + gridDim.x;
+        item = t < (unsigned int)p.n_items ? (int)t : -1;
       }
       item = __shfl_sync(0xffffffffu, item, 0);
+      FwdItem it = {};
+      if (item >= 0) it = fwd_decode_item(p, item);
+      if (lane == 0) {
+        if (item >= 0) fwd_publish_item(item_ring + 16 * slot, item, it);
+        else item_ring[16 * slot] = -1;
+        mbar_arrive(bar(L::kItemFull + slot));  // (release: the record is visible to whoever sees the phase)
+      }
       if (item < 0) break;
-      const FwdItem it = fwd_decode_item(p, item);
       if (it.n_max == 0) continue;
 
       // Q tiles of this item: the previous item's score products must have read theirs
@@ -487,9 +508,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     int total = 0;                 // jobs issued so far, saturating at kSBufs
     bool ok = true;
     for (int k = 0; ok; ++k) {
-      const int item = read_item(k);
+      FwdItem it;
+      const int item = read_item(k, it);
       if (item < 0) break;
-      const FwdItem it = fwd_decode_item(p, item);
       if (it.n_max == 0) continue;
       const int n0 = it.n0, n1 = it.n1;
       const int n_jobs = n0 + n1;
@@ -591,9 +612,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       };
 
       for (int k = 0; ok; ++k) {
-        const int item = read_item(k);
+        FwdItem it;
+        const int item = read_item(k, it);
         if (item < 0) break;
-        const FwdItem it = fwd_decode_item(p, item);
         if (it.n_max == 0) continue;
         n0 = it.n0;
         n1 = it.n1;
@@ -639,9 +660,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     int act = 0;            // items with work so far
     bool ok = true;
     for (int k = 0; ok; ++k) {
-      const int item = read_item(k);
+      FwdItem it;
+      const int item = read_item(k, it);
       if (item < 0) break;
-      const FwdItem it = fwd_decode_item(p, item);
       if (it.n_max == 0) continue;
       const int n0 = it.n0, n1 = it.n1;
       const int n_jobs = n0 + n1;
@@ -694,24 +715,24 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     bool ok = true;
 
     for (int k = 0; ok; ++k) {
-      // The ring slot keeps the item until this warp releases it at the end of the item, so what
-      // only the epilogue needs is decoded again there instead of being held in registers.
+      // The ring slot keeps the item's record until this warp releases it at the end of the item, so what
+      // only the epilogue needs is read again there instead of being held in registers.
       const int islot = k & 1;
       ok = mbar_wait_warp(bar(L::kItemFull + islot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30);
       if (!ok) break;
-      const int item = item_ring[islot];
+      const int item = item_ring[16 * islot];
       if (item < 0) break;
       int n0, n1, q0, Lk;
       float c0;
       const float* sm_row = nullptr;
       int sm_lim = 0;
       {
-        const FwdItem it = fwd_decode_item(p, item);
+        const FwdItem it = fwd_load_item(item_ring + 16 * islot);
         n0 = it.n0;
         n1 = it.n1;
         q0 = it.q0;
         Lk = it.Lk;
-        c0 = (p.bias ? p.bias[it.b] : p.bias_scalar) * kLog2e;
+        c0 = it.bias * kLog2e;
         if constexpr (kScoreMod) {
           sm_row = p.score_mod + (p.cu_k ? (int64_t)it.tk0 : (int64_t)it.b * p.Tk);
           sm_lim = it.key_lim;
@@ -799,7 +820,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
 
       // ---------------------------------------------------------- epilogue of the item
       // Every warp takes its lane quarter and a quarter of the head dimension of BOTH query tiles.
-      const FwdItem it = fwd_decode_item(p, item_ring[islot]);
+      const FwdItem it = fwd_load_item(item_ring + 16 * islot);
       constexpr int kDMine = D / 4;  // output columns per thread and tile
       uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) +
                         2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)(it.tq0 + it.q0) * p.o_st) +
