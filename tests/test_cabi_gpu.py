@@ -96,3 +96,41 @@ def test_event_hooks_time_the_main_kernel():
     for direction in ("fwd", "bwd"):
         ms = time_main_kernel(direction, q, k, v, do, iters=3)
         assert len(ms) == 3 and all(0 < x < 100 for x in ms)
+
+
+def test_forward_launch_replays_from_a_cuda_graph():
+    """A forward call recorded into a stream capture (after a first, ordinary call on the device) replays
+    with the same result; launches made under capture draw their work-item counters from a pool of their own."""
+    lib = _cabi.load()
+    torch.manual_seed(3)
+    B, T, H, D = 2, 384, 2, 64
+    q, k, v = [torch.randn(B, T, H, D, device="cuda", dtype=torch.bfloat16) * 0.5 for _ in range(3)]
+    eager = torch.empty_like(q)
+    replayed = torch.full_like(q, float("nan"))
+
+    def params(o, stream):
+        p = _cabi.SigAttnParams()
+        p.struct_bytes = ctypes.sizeof(p)
+        p.dtype, p.B, p.H, p.D, p.Tq, p.Tk = _cabi.SIGATTN_BF16, B, H, D, T, T
+        p.flags = _cabi.SIGATTN_CAUSAL
+        p.scale, p.bias_scalar, p.device = 1.0 / math.sqrt(D), -math.log(T), 0
+        p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+        for name in ("q", "k", "v", "o"):
+            setattr(p, name + "_strides", _s3(q))
+        p.stream = stream
+        return p
+
+    p0 = params(eager, torch.cuda.current_stream().cuda_stream)
+    assert lib.sigattn_fwd(ctypes.byref(p0)) == 0, lib.sigattn_last_error()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.graph(graph, stream=side):
+        p1 = params(replayed, torch.cuda.current_stream().cuda_stream)
+        assert lib.sigattn_fwd(ctypes.byref(p1)) == 0, lib.sigattn_last_error()
+    for _ in range(3):
+        replayed.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(replayed, eager)
+    assert lib.sigattn_device_status(0) == 0

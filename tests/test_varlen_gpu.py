@@ -135,3 +135,23 @@ def test_float32_sequences():
         rd = orc.sigattn_backward(*args, do[sq][None], work=torch.float64)
         for g, r in ((q.grad[sq], rd[0][0]), (k.grad[sk], rd[1][0]), (v.grad[sk], rd[2][0])):
             assert rel_l2(g.double().cpu(), r) <= 1e-5
+
+
+def test_rows_outside_the_sequences_stay_zero():
+    """Packed buffers larger than the sequences (rows behind the last one), gaps between sequences and an
+    understated max_seqlen_q: the rows no sequence covers come back as zeros in the output and in dQ."""
+    H, D = 2, 64
+    # sequences at rows [0, 100), [128, 190) (a gap of 28 rows), 10 spare rows at the end
+    cu_q = torch.tensor([0, 100, 190], dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0, 100, 190], dtype=torch.int32, device="cuda")
+    total = 200
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q, k, v, do = [(torch.randn(total, H, D, device="cuda", generator=g) * 0.5).half() for _ in range(4)]
+    for t in (q, k, v):
+        t.requires_grad_()
+    out = m.sigmoid_attention_varlen(q, k, v, cu_q, cu_k, 64, 100)  # second sequence has 90 queries: cut at 64
+    out.backward(do)
+    assert torch.isfinite(out).all() and torch.isfinite(q.grad).all()
+    assert out[190:].abs().max().item() == 0 and q.grad[190:].abs().max().item() == 0       # behind the sequences
+    assert out[164:190].abs().max().item() == 0 and q.grad[164:190].abs().max().item() == 0  # beyond max_seqlen_q
+    assert out[:64].abs().max().item() > 0 and out[100:164].abs().max().item() > 0

@@ -55,6 +55,28 @@ EncodeTiledFn get_encode_fn() {
 // Rows at or beyond T read as zeros.
 int make_map(CUtensorMap* m, const void* base, int dtype, int B, int T, int H, int D, const int64_t* strides,
              int box_rows, const char* name) {
+  // Encoding a tensor map is a driver call of a microsecond or two, and a training loop calls with the same
+  // tensors (or the same allocator blocks) again and again: a small per-thread cache keyed by everything the
+  // encoding depends on.
+  struct Key {
+    const void* base;
+    int dtype, B, T, H, D, box_rows;
+    int64_t s0, s1, s2;
+    bool operator==(const Key& o) const {
+      return base == o.base && dtype == o.dtype && B == o.B && T == o.T && H == o.H && D == o.D && box_rows == o.box_rows &&
+             s0 == o.s0 && s1 == o.s1 && s2 == o.s2;
+    }
+  };
+  constexpr int kCacheEntries = 16;
+  struct Entry { Key key; CUtensorMap map; bool valid; };
+  thread_local Entry cache[kCacheEntries] = {};
+  thread_local int next_victim = 0;
+  const Key key{base, dtype, B, T, H, D, box_rows, strides[0], strides[1], strides[2]};
+  for (int i = 0; i < kCacheEntries; ++i)
+    if (cache[i].valid && cache[i].key == key) {
+      *m = cache[i].map;
+      return 0;
+    }
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return fail(-101, "cuTensorMapEncodeTiled is not available from this driver");
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return fail(-3, "%s: base pointer must be 16-byte aligned", name);
@@ -70,6 +92,11 @@ int make_map(CUtensorMap* m, const void* base, int dtype, int B, int T, int H, i
                    const_cast<void*>(base), dims, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-102, "%s: cuTensorMapEncodeTiled failed with CUresult %d", name, (int)r);
+  Entry& e = cache[next_victim];
+  next_victim = (next_victim + 1) % kCacheEntries;
+  e.key = key;
+  e.map = *m;
+  e.valid = true;
   return 0;
 }
 
