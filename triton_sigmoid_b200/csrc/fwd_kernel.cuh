@@ -7,7 +7,7 @@
 // (src/triton_sigmoid/sigmoid_triton_dense.py:23-154) and _fwd_padded_kernel
 // (src/triton_sigmoid/sigmoid_triton_padded.py:24-171).
 //
-// Structure (sm_100a, 20 warps):
+// Structure (sm_100a, 24 warps):
 //   warps 0-15   sigmoid warps.  A JOB is one query tile (128 rows) times one key tile (128 columns);
 //                one thread per row, 32-column chunks, P written over the start of the chunk's columns.
 //                D = 128: all sixteen warps work on the same job (warp w: TMEM lanes 32 (w & 3) ..,
@@ -23,6 +23,10 @@
 //   warp  16     item scheduler + TMA producer: Q tiles per item, K_j / V_j through a ring of smem stages
 //   warp  17     tcgen05 issuer 1: S = Q_s K_j^T (smem x smem -> TMEM fp32); owns the TMEM allocation
 //   warp  18     tcgen05 issuer 2: O_s += P V_j (TMEM x smem -> TMEM fp32)
+//   warps 20-23  output warps (one per TMEM lane quarter): wait for an item's last P V product, read O out of
+//                TMEM, round it and write it to global memory, while the sigmoid warps are already at work
+//                on the next item's scores (measured against the sigmoid warps writing O themselves:
+//                +8 % at N = 512, +3 % at N = 1024-2048, +1 % at N = 4096)
 // There is no row normaliser in sigmoid attention, so O simply accumulates in TMEM over the
 // whole key loop of an item.  The (query tile, key tile) jobs are processed in a fixed order through a
 // small ring of S buffers in TMEM (3 when D = 64, 2 when D = 128): the issuer computes the
@@ -65,13 +69,16 @@ constexpr int kFwdSigmoidWarps = 16;
 constexpr int kFwdProducerWarp = kFwdSigmoidWarps;
 constexpr int kFwdIssuerWarp = kFwdSigmoidWarps + 1;   // S = Q K^T, owns the TMEM allocation
 constexpr int kFwdIssuerWarp2 = kFwdSigmoidWarps + 2;  // O += P V
-constexpr int kFwdThreads = (kFwdSigmoidWarps + 4) * 32;  // the role warps form a register-allocation group of four
-constexpr int kFwdLaunchRegs = 96;  // what 640 threads per CTA get each: 65536 / 640, rounded down to a multiple of 8
-// Registers per thread after the re-allocation: the role warps (a group of four) and the sigmoid warps.
+constexpr int kFwdOutputWarp0 = kFwdSigmoidWarps + 4;  // four output warps, one per TMEM lane quarter
+constexpr int kFwdThreads = (kFwdSigmoidWarps + 8) * 32;  // role warps and output warps: two register-allocation groups of four
+constexpr int kFwdLaunchRegs = 80;  // what 768 threads per CTA get each: 65536 / 768, rounded down to a multiple of 8
+// Registers per thread after the re-allocation: the role warps, the output warps (a group of four each)
+// and the sigmoid warps.
 template <int D> struct FwdRegs {
-  static constexpr int kRole = (D == 64) ? 32 : 40;
-  static constexpr int kSigmoid = (D == 64) ? 112 : 104;
-  static_assert(kFwdSigmoidWarps * 32 * kSigmoid + 128 * kRole <= kFwdThreads * kFwdLaunchRegs,
+  static constexpr int kRole = 32;
+  static constexpr int kOutput = 32;
+  static constexpr int kSigmoid = 104;
+  static_assert(kFwdSigmoidWarps * 32 * kSigmoid + 128 * kRole + 128 * kOutput <= kFwdThreads * kFwdLaunchRegs,
                 "the re-allocation may not ask for more registers than the CTA holds");
 };
 constexpr int kFwdBlockM = 256;  // query rows per CTA (two 128-row tiles)
@@ -320,12 +327,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   constexpr uint32_t kColS = 0;              // S buffer i at kColS + 128 i
   constexpr uint32_t kColO = 128 * kSBufs;   // O_s at kColO + D s
   constexpr int kSiteBase = 0x10000;
-  // D = 64: scores and P V are issued by two warps (the issue stream bounds the kernel); D = 128:
-  // one warp issues both, in order - with only two S buffers the extra barrier hop costs more
-  constexpr bool kSplitIssue = true;
   constexpr int kJobWarps = (D == 64) ? 8 : 16;  // sigmoid warps per job (see the file header)
-  // warps that read the published item index: the sigmoid warps and the issuing warp(s)
-  constexpr int kItemReaders = kFwdSigmoidWarps + (kSplitIssue ? 2 : 1);
+  // warps that read the published item record: the sigmoid warps, the two issuing warps, the output warps
+  constexpr int kItemReaders = kFwdSigmoidWarps + 2 + 4;
   static_assert(kColO + 2 * D <= kTmemCols, "TMEM budget");
 
   extern __shared__ uint8_t smem_dyn[];
@@ -362,7 +366,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     mbar_init(bar(L::kOFull), 1);
     for (int i = 0; i < kStages; ++i) mbar_init(bar(L::kVFix + i), 1);
     mbar_init(bar(L::kQEmpty), 1);
-    mbar_init(bar(L::kOEmpty), kFwdSigmoidWarps);
+    mbar_init(bar(L::kOEmpty), 4);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(L::kItemFull + i), 1);
       mbar_init(bar(L::kItemEmpty + i), kItemReaders);
@@ -384,8 +388,8 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
   const uint32_t tmem = *tmem_slot;
 
   // The sigmoid warps hold 64 scores each in flight and want more registers than an even split
-  // gives; the four role warps need few.  Registers only move within what the CTA was given at
-  // launch, so the two counts must add up to no more than that (else the increase never returns).
+  // gives; the role warps and the output warps need few.  Registers only move within what the CTA was
+  // given at launch, so the counts must add up to no more than that (else the increase never returns).
 
   // Consumer side of the item ring: returns the k-th item of this CTA, or -1 when there is none
   // (also on a failed wait).  Called by all 32 lanes of a reader warp.
@@ -399,7 +403,75 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     return item;
   };
 
-  if (warp >= kFwdSigmoidWarps) {
+  if (warp >= kFwdOutputWarp0) {
+    // ============================================================ output warps: O from TMEM to global memory
+    // Four warps, one per TMEM lane quarter (a warp can only read the lanes 32 (warp % 4) ..), one thread
+    // per query row.  They take the finished accumulators of an item off the sigmoid warps' hands: those go
+    // straight on to the next item's scores while the last P V products complete and O is written out.
+    setmaxnreg_dec<FwdRegs<D>::kOutput>();
+    const int lane_row = (warp & 3) * 32 + lane;
+    const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    int act = 0;  // items with work so far
+    bool ok = true;
+    for (int k = 0; ok; ++k) {
+      const int islot = k & 1;
+      ok = mbar_wait_warp(bar(L::kItemFull + islot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30);
+      if (!ok) break;
+      const volatile int* rec = item_ring + 16 * islot;
+      if (rec[0] < 0) break;
+      const FwdItem it = fwd_load_item(rec);
+      uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) +
+                        2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)(it.tq0 + it.q0 + lane_row) * p.o_st);
+      if (it.n_max > 0) {
+        ok = mbar_wait_warp(bar(L::kOFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 12);
+        if (!ok) break;
+        ++act;
+        tc_fence_after_sync();
+      }
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const int row = it.q0 + 128 * s + lane_row;
+        const bool in_rows = row < it.row_lim;  // rows this item may write at all
+        const bool live = row < it.Lq;          // rows beyond the valid length are written as zeros
+        uint8_t* o_row = o_base + 2 * (int64_t)(128 * s) * p.o_st;
+        if ((s == 0 ? it.n0 : it.n1) > 0) {
+          const uint32_t o_addr = tmem_lane + kColO + D * s;
+#pragma unroll
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld16(o_addr + 16 * c, r);
+            tmem_ld_wait_for(r);
+            uint4 w0, w1;
+            w0.x = pack2<kBF16>(__uint_as_float(r[0]), __uint_as_float(r[1]));
+            w0.y = pack2<kBF16>(__uint_as_float(r[2]), __uint_as_float(r[3]));
+            w0.z = pack2<kBF16>(__uint_as_float(r[4]), __uint_as_float(r[5]));
+            w0.w = pack2<kBF16>(__uint_as_float(r[6]), __uint_as_float(r[7]));
+            w1.x = pack2<kBF16>(__uint_as_float(r[8]), __uint_as_float(r[9]));
+            w1.y = pack2<kBF16>(__uint_as_float(r[10]), __uint_as_float(r[11]));
+            w1.z = pack2<kBF16>(__uint_as_float(r[12]), __uint_as_float(r[13]));
+            w1.w = pack2<kBF16>(__uint_as_float(r[14]), __uint_as_float(r[15]));
+            if (!live) w0 = w1 = make_uint4(0, 0, 0, 0);
+            if (in_rows) {
+              *reinterpret_cast<uint4*>(o_row + 32 * c) = w0;
+              *reinterpret_cast<uint4*>(o_row + 32 * c + 16) = w1;
+            }
+          }
+        } else if (in_rows) {
+          // this tile is entirely padding: zero rows
+#pragma unroll
+          for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      if (it.n_max > 0) {
+        // O has left TMEM: the next item's products may overwrite the accumulators
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kOEmpty));
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(L::kItemEmpty + islot));
+    }
+  } else if (warp >= kFwdSigmoidWarps) {
   // All four role warps (the idle one included) execute this one instruction: the release is an
   // operation of the whole group of four.
   setmaxnreg_dec<FwdRegs<D>::kRole>();
@@ -489,7 +561,6 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     }
   }
   else if (warp == kFwdIssuerWarp) {
-    if constexpr (kSplitIssue) {
     // ============================================================ tcgen05 issuer 1: S = Q K^T
     // Two issuing warps (this one for the scores, the next for P V): an issuing warp's
     // instruction stream is one long dependent chain (waits, MMAs, commits), and a single warp
@@ -541,113 +612,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       if (n0 > 0) q_par0 ^= 1u;
       if (n1 > 0) q_par1 ^= 1u;
     }
-    } else {
-    // ============================================================ single tcgen05 issuer (D = 128)
-    // This warp's instruction stream is one long dependent chain, so its length per job decides
-    // how quickly finished probabilities turn into new scores: all ring positions, stage numbers
-    // and barrier parities are carried incrementally (no division, no modulo) and run on across
-    // items; descriptors are a precomputed base plus a constant in the start-address field.
-    {
-      const bool leader = elect_one();
-      constexpr uint32_t idesc_qk = make_idesc(128, 128, kBF16, false, false);
-      constexpr uint32_t idesc_pv = make_idesc(128, D, kBF16, false, true);
-      constexpr uint32_t kStageStep = kTileBytes >> 4;  // one smem stage, in descriptor address units
-      bool ok = true;
-      // Q tile 0, K stage 0 (rows = M/N, the 64 contiguous elements = K) and V stage 0 (rows = K,
-      // the 64 contiguous elements = N, next 64-column block 16 KB further)
-      const uint64_t q_desc0 = smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
-      const uint64_t k_desc0 = smem_desc_sw128(smem_base + L::kKOff, 16, 1024);
-      const uint64_t v_desc0 = smem_desc_sw128(smem_base + L::kVOff, 16384, 1024);
-      const uint32_t q_lo = (uint32_t)q_desc0, q_hi = (uint32_t)(q_desc0 >> 32);
-      const uint32_t k_lo = (uint32_t)k_desc0, k_hi = (uint32_t)(k_desc0 >> 32);
-      const uint32_t v_lo = (uint32_t)v_desc0, v_hi = (uint32_t)(v_desc0 >> 32);
-
-      FwdCursor cs{0, 0, 0, 0u, 0, 0u, true};  // next scores to issue
-      FwdCursor cp = cs;                       // next P V product to issue
-      uint32_t q_par0 = 0u, q_par1 = 0u;       // parity of each Q tile's "full" barrier
-      uint32_t fix_par = 0u;                   // bit st: parity of stage st's "padded V rows cleared" barrier
-      int act = 0;                             // items with work so far
-      int n0 = 0, n1 = 0, Lk = 0;
-
-      // S[buf] = Q_s K_j^T
-      auto issue_s = [&](const FwdCursor& c) {
-        if (c.j == 0) ok = ok && mbar_wait_warp(bar(L::kQFull + c.s), (c.s ? q_par1 : q_par0), abort_flag, kSiteBase + 3);
-        if (c.fresh) ok = ok && mbar_wait_warp(bar(L::kKFull + c.st), c.ph, abort_flag, kSiteBase + 5);
-        if (!ok) return;
-        const uint32_t qa = q_lo + (uint32_t)c.s * kStageStep;
-        const uint32_t ka = k_lo + (uint32_t)c.st * kStageStep;
-        const uint32_t dst = tmem + kColS + 128u * (uint32_t)c.buf;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (uint32_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
-          mma_ss(leader, dst, make_desc(qa + off, q_hi), make_desc(ka + off, k_hi), idesc_qk, kk > 0);
-        }
-        mma_commit(leader, bar(L::kSFull + c.buf));
-        // last job that reads K_j: hand the stage back to the producer
-        if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kKEmpty + c.st));
-      };
-      // O_s += P[buf] V_j
-      auto issue_pv = [&](const FwdCursor& c) {
-        if (c.fresh) {
-          ok = ok && mbar_wait_warp(bar(L::kVFull + c.st), c.ph, abort_flag, kSiteBase + 6);
-          if (c.j * kTileN + kTileN > Lk) {  // padded V rows are being cleared by the producer warp
-            ok = ok && mbar_wait_warp(bar(L::kVFix + c.st), (fix_par >> c.st) & 1u, abort_flag, kSiteBase + 14);
-            fix_par ^= 1u << c.st;
-          }
-        }
-        ok = ok && mbar_wait_warp(bar(L::kPFull + c.buf), c.bph, abort_flag, kSiteBase + 7);
-        if (!ok) return;
-        tc_fence_after_sync();
-        const uint32_t va = v_lo + (uint32_t)c.st * kStageStep;
-        const uint32_t pa = tmem + kColS + 128u * (uint32_t)c.buf;
-        const uint32_t dst = tmem + kColO + (uint32_t)(D * c.s);
-        const uint32_t acc0 = c.j > 0 ? 1u : 0u;
-#pragma unroll
-        for (int kk = 0; kk < kTileN / 16; ++kk) {
-          // P of key columns [32g, 32g+32) sits, 16-bit packed, in buffer columns 32g + [0,16)
-          mma_ts(leader, dst, pa + 32 * (kk >> 1) + 8 * (kk & 1), make_desc(va + kk * (2048 >> 4), v_hi), idesc_pv,
-                 kk > 0 ? 1u : acc0);
-        }
-        if (c.s == 1 || c.j >= n1) mma_commit(leader, bar(L::kVEmpty + c.st));
-      };
-
-      for (int k = 0; ok; ++k) {
-        FwdItem it;
-        const int item = read_item(k, it);
-        if (item < 0) break;
-        if (it.n_max == 0) continue;
-        n0 = it.n0;
-        n1 = it.n1;
-        Lk = it.Lk;
-        const int n_jobs = n0 + n1;
-        cs.begin_item(n0);
-        cp.begin_item(n0);
-        int n_s = 0;
-        // scores of the next job; after the item's last ones the Q tiles may be overwritten, which
-        // lets the producer fetch the next item's while the remaining products run
-        auto next_s = [&]() {
-          issue_s(cs);
-          cs.advance(n0, n1, kStages, kSBufs);
-          if (++n_s == n_jobs && ok) mma_commit(leader, bar(L::kQEmpty));
-        };
-        while (n_s < kSBufs && n_s < n_jobs && ok) next_s();
-        // the accumulators still hold the previous item's O until the sigmoid warps have read it
-        if (act > 0) ok = ok && mbar_wait_warp(bar(L::kOEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 33);
-        for (int n = 0; n < n_jobs && ok; ++n) {
-          issue_pv(cp);
-          cp.advance(n0, n1, kStages, kSBufs);
-          if (n_s < n_jobs && ok) next_s();  // reuses the buffer the product above has just consumed
-        }
-        if (!ok) break;
-        mma_commit(leader, bar(L::kOFull));
-        if (n0 > 0) q_par0 ^= 1u;
-        if (n1 > 0) q_par1 ^= 1u;
-        ++act;
-      }
-    }
-    }
   } else if (warp == kFwdIssuerWarp2) {
-    if constexpr (kSplitIssue) {
     // ============================================================ tcgen05 issuer 2: O_s += P V_j
     const bool leader = elect_one();
     constexpr uint32_t idesc_pv = make_idesc(128, D, kBF16, false, true);
@@ -698,11 +663,10 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       mma_commit(leader, bar(L::kOFull));
       ++act;
     }
-    }
   }
   }  // role warps
   else {
-    // ============================================================ sigmoid warps + epilogue
+    // ============================================================ sigmoid warps
     setmaxnreg_inc<FwdRegs<D>::kSigmoid>();
     const int cq = warp >> 2;                         // quarter of a job's key columns (16 warps per job) / of the head dimension in the epilogue
     const int lane_row = (warp & 3) * 32 + lane;      // TMEM lane == row within a query tile
@@ -711,12 +675,9 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     int buf = 0;          // 16 warps per job: S buffer of the next job
     uint32_t bph = 0u;    //                   and the parity of that buffer's barriers
     int jobs_base = 0;    // 8 warps per job: jobs of all earlier items, position of this item's first job in the S ring
-    int act = 0;          // items with work so far
     bool ok = true;
 
     for (int k = 0; ok; ++k) {
-      // The ring slot keeps the item's record until this warp releases it at the end of the item, so what
-      // only the epilogue needs is read again there instead of being held in registers.
       const int islot = k & 1;
       ok = mbar_wait_warp(bar(L::kItemFull + islot), (uint32_t)(k >> 1) & 1u, abort_flag, kSiteBase + 30);
       if (!ok) break;
@@ -738,6 +699,8 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           sm_lim = it.key_lim;
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(L::kItemEmpty + islot));  // the record is in registers
       // per query tile: largest visible key index of this thread's row, and the first key index at which a
       // chunk needs the element predicate (it reaches beyond the keys every row of the tile sees)
       int lim[2], mask_from[2];
@@ -818,73 +781,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       }
       if (!ok) break;
 
-      // ---------------------------------------------------------- epilogue of the item
-      // Every warp takes its lane quarter and a quarter of the head dimension of BOTH query tiles.
-      const FwdItem it = fwd_load_item(item_ring + 16 * islot);
-      constexpr int kDMine = D / 4;  // output columns per thread and tile
-      uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) +
-                        2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)(it.tq0 + it.q0) * p.o_st) +
-                        2 * cq * kDMine;
-      uint4 w[2][kDMine / 8];
-      if (n_max > 0) {
-        ok = mbar_wait_warp(bar(L::kOFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 12);
-        if (!ok) break;
-        ++act;
-        tc_fence_after_sync();
-        // O leaves TMEM already rounded to 16 bits, so that few registers are live across the hand-over
-#pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          if ((s == 0 ? n0 : n1) > 0) {
-            const uint32_t o_addr = tmem_lane + kColO + D * s + cq * kDMine;
-            const bool live = it.q0 + 128 * s + lane_row < it.Lq;
-            if constexpr (kDMine == 32) {
-              uint32_t r[32];
-              tmem_ld32_sync(o_addr, r);
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
-                w[s][q4].x = pack2<kBF16>(__uint_as_float(r[8 * q4 + 0]), __uint_as_float(r[8 * q4 + 1]));
-                w[s][q4].y = pack2<kBF16>(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3]));
-                w[s][q4].z = pack2<kBF16>(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5]));
-                w[s][q4].w = pack2<kBF16>(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7]));
-                if (!live) w[s][q4] = make_uint4(0, 0, 0, 0);
-              }
-            } else {
-              uint32_t r[16];
-              tmem_ld16(o_addr, r);
-              tmem_ld_wait_for(r);
-#pragma unroll
-              for (int q4 = 0; q4 < 2; ++q4) {
-                w[s][q4].x = pack2<kBF16>(__uint_as_float(r[8 * q4 + 0]), __uint_as_float(r[8 * q4 + 1]));
-                w[s][q4].y = pack2<kBF16>(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3]));
-                w[s][q4].z = pack2<kBF16>(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5]));
-                w[s][q4].w = pack2<kBF16>(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7]));
-                if (!live) w[s][q4] = make_uint4(0, 0, 0, 0);
-              }
-            }
-          }
-        }
-        // O is in registers: the next item's products may overwrite the accumulators
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kOEmpty));
-      }
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const int row = it.q0 + 128 * s + lane_row;
-        if (row < it.row_lim) {
-          uint8_t* o_row = o_base + 2 * (int64_t)(128 * s + lane_row) * p.o_st;
-          if ((s == 0 ? n0 : n1) > 0) {
-#pragma unroll
-            for (int q4 = 0; q4 < kDMine / 8; ++q4) *reinterpret_cast<uint4*>(o_row + 16 * q4) = w[s][q4];
-          } else {
-            // this tile is entirely padding: zero rows
-#pragma unroll
-            for (int q4 = 0; q4 < kDMine / 8; ++q4) *reinterpret_cast<uint4*>(o_row + 16 * q4) = make_uint4(0, 0, 0, 0);
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(L::kItemEmpty + islot));
+      // the item's accumulators are the output warps' business; on to the next item
     }
   }
 

@@ -139,20 +139,23 @@ def _base_params(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_cau
     p.B, p.H, p.D, p.Tq, p.Tk = B, H, D, Tq, k.shape[1]
     p.flags = _flags(is_causal)
     p.scale = float(scale)
-    p.bias_scalar = 0.0
     p.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.q_strides, p.k_strides, p.v_strides = _strides3(q), _strides3(k), _strides3(v)
     p.seq_lens_q = seq_lens_q.data_ptr() if seq_lens_q is not None else None
     p.seq_lens_k = seq_lens_k.data_ptr() if seq_lens_k is not None else None
-    p.bias = bias.data_ptr()
+    if isinstance(bias, torch.Tensor):  # one value per batch element
+        p.bias, p.bias_scalar = bias.data_ptr(), 0.0
+    else:                               # one value for the whole call: no device tensor needed
+        p.bias, p.bias_scalar = None, float(bias)
     p.score_mod = score_mod.data_ptr() if score_mod is not None else None
     p.stream = torch.cuda.current_stream(q.device).cuda_stream
     return p
 
 
 def _prep_aux(q, bias, score_mod, seq_lens_q, seq_lens_k):
-    bias = bias.to(device=q.device, dtype=torch.float32).contiguous()
+    if isinstance(bias, torch.Tensor):
+        bias = bias.to(device=q.device, dtype=torch.float32).contiguous()
     if score_mod is not None:
         score_mod = score_mod.to(device=q.device, dtype=torch.float32).contiguous()
     if seq_lens_q is not None:
@@ -291,6 +294,37 @@ def _padded_backward(ctx, dO):
 
 
 sigmoid_attn_padded_fwd_op.register_autograd(_padded_backward, setup_context=_padded_setup_context)
+
+
+# ----------------------------------------------------------------------------- eager shortcut
+class _EagerSigmoidAttention(torch.autograd.Function):
+    """What the dense and padded ops do, minus the dispatcher: in eager mode the public functions call the
+    library through this plain autograd function, because a `torch.library.custom_op` round trip with its
+    generated autograd wrapper costs about 100 us of host time per forward + backward pair, which is more
+    than the kernels of a short-sequence call take.  Under `torch.compile` the public functions use the
+    registered ops (fake kernels, autograd registration) instead.  `bias` is a [B] tensor or a Python
+    float (one value for the whole call, passed by value)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal):
+        bias_t = bias if isinstance(bias, torch.Tensor) else None
+        ctx.save_for_backward(q, k, v, bias_t, score_mod, seq_lens_q, seq_lens_k)
+        ctx.bias_value = None if bias_t is not None else bias
+        ctx.scale, ctx.is_causal = scale, is_causal
+        return _run_fwd(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal)
+
+    @staticmethod
+    def backward(ctx, dO):
+        q, k, v, bias_t, score_mod, seq_lens_q, seq_lens_k = ctx.saved_tensors
+        bias = bias_t if bias_t is not None else ctx.bias_value
+        dq, dk, dv = _run_bwd(q, k, v, dO, bias, score_mod, seq_lens_q, seq_lens_k, ctx.scale, ctx.is_causal)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def _eager_attention(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal):
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return _EagerSigmoidAttention.apply(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal)
+    return _run_fwd(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal)
 
 
 # ----------------------------------------------------------------------------- packed (variable-length) ops
@@ -476,17 +510,15 @@ def sigmoid_attention(
     Dk = _kernel_head_dim(D)
     query, key, value = (_pad_head_dim(t, Dk).contiguous() for t in (query, key, value))
 
+    bias_value = float(sigmoid_bias) if sigmoid_bias is not None else (-math.log(float(T_q)) if T_q > 0 else 0.0)
     if torch.compiler.is_compiling():
         for x in (query, key, value):
             torch._dynamo.mark_static(x, -2)  # heads
             torch._dynamo.mark_static(x, -1)  # head dimension
-
-    if sigmoid_bias is None:
-        bias = torch.full((B,), -math.log(float(T_q)) if T_q > 0 else 0.0, dtype=torch.float32, device=query.device)
+        bias = torch.full((B,), bias_value, dtype=torch.float32, device=query.device)
+        out = sigmoid_attention_fwd_op(query, key, value, bias, score_mod, float(scale), bool(is_causal))
     else:
-        bias = torch.full((B,), float(sigmoid_bias), dtype=torch.float32, device=query.device)
-
-    out = sigmoid_attention_fwd_op(query, key, value, bias, score_mod, float(scale), bool(is_causal))
+        out = _eager_attention(query, key, value, bias_value, score_mod, None, None, float(scale), bool(is_causal))
     return out if Dk == D else out[..., :D]
 
 
@@ -514,8 +546,11 @@ def sigmoid_attention_padded(
     if T_k != T_v:
         raise ValueError(f"Key and value sequence lengths must match, got K={T_k}, V={T_v}")
 
+    compiling = torch.compiler.is_compiling()
+    full_k = seq_lens_k is None
     if seq_lens_k is None:
-        seq_lens_k = torch.full((B,), T_k, dtype=torch.int32, device=query.device)
+        if compiling:  # the op's schema wants tensors; the eager path passes "all valid" as a null pointer
+            seq_lens_k = torch.full((B,), T_k, dtype=torch.int32, device=query.device)
     else:
         if seq_lens_k.shape != (B,):
             raise ValueError(f"seq_lens_k must have shape ({B},), got {seq_lens_k.shape}")
@@ -523,7 +558,8 @@ def sigmoid_attention_padded(
             seq_lens_k = seq_lens_k.to(torch.int32)
         seq_lens_k = seq_lens_k.to(query.device).contiguous()
     if seq_lens_q is None:
-        seq_lens_q = torch.full((B,), T_q, dtype=torch.int32, device=query.device)
+        if compiling:
+            seq_lens_q = torch.full((B,), T_q, dtype=torch.int32, device=query.device)
     else:
         if seq_lens_q.shape != (B,):
             raise ValueError(f"seq_lens_q must have shape ({B},), got {seq_lens_q.shape}")
@@ -542,19 +578,24 @@ def sigmoid_attention_padded(
     Dk = _kernel_head_dim(D)
     query, key, value = (_pad_head_dim(t, Dk).contiguous() for t in (query, key, value))
 
-    if torch.compiler.is_compiling():
+    if sigmoid_bias is not None:
+        bias = float(sigmoid_bias)
+    elif full_k:
+        bias = -math.log(float(T_k)) if T_k > 0 else float("inf")
+    else:
+        # -log(0) = +inf for an empty key set; every probability is masked there anyway
+        bias = -torch.log(seq_lens_k.clamp(min=0, max=T_k).float())
+
+    if compiling:
         for x in (query, key, value):
             torch._dynamo.mark_static(x, -2)  # heads
             torch._dynamo.mark_static(x, -1)  # head dimension
-
-    if sigmoid_bias is None:
-        # -log(0) = +inf for an empty key set; every probability is masked there anyway
-        bias = -torch.log(seq_lens_k.clamp(min=0, max=T_k).float())
+        if not isinstance(bias, torch.Tensor):
+            bias = torch.full((B,), bias, dtype=torch.float32, device=query.device)
+        out = sigmoid_attn_padded_fwd_op(query, key, value, seq_lens_k, seq_lens_q, bias, score_mod, float(scale),
+                                         bool(is_causal))
     else:
-        bias = torch.full((B,), float(sigmoid_bias), dtype=torch.float32, device=query.device)
-
-    out = sigmoid_attn_padded_fwd_op(query, key, value, seq_lens_k, seq_lens_q, bias, score_mod, float(scale),
-                                     bool(is_causal))
+        out = _eager_attention(query, key, value, bias, score_mod, seq_lens_q, seq_lens_k, float(scale), bool(is_causal))
     return out if Dk == D else out[..., :D]
 
 
