@@ -145,3 +145,29 @@ def test_many_items_with_mixed_lengths_against_gpu_fp32_math(D, dtype, causal):
         assert torch.isfinite(g).all()
         assert g[~valid].abs().max().item() == 0
         assert rel_l2(g[valid], r[valid]) <= 1e-2
+
+
+@pytest.mark.parametrize("D,dtype", [(64, torch.float16), (128, torch.bfloat16)])
+def test_query_tile_without_work_for_many_items(D, dtype):
+    """Cross-attention with 256 query slots of which most batch elements use only the first 128 (so the second
+    query tile of their work items has no keys at all) against 640 keys, a few full ones in between: in the
+    forward kernel the warps of the second query tile then sit out whole items while the first tile's run
+    through five jobs each, and must still be in step with the score buffers when their next job comes.
+    Repeated, since the order of items per SM depends on timing."""
+    B, Tq, Tk, H = 48, 256, 640, 8
+    lq = torch.full((B,), 128, dtype=torch.int32)
+    lq[5::7] = 256
+    lq[11] = 129
+    lq = lq.cuda()
+    lk = torch.full((B,), Tk, dtype=torch.int32, device="cuda")
+    q, k, v, _ = make_inputs(B, Tq, Tk, H, D, dtype, std=0.5, seed=D)
+    qf, kf, vf = q.float(), k.float(), v.float()
+    ref = m.sigmoid_attention_ref(qf, kf, vf, seq_lens_k=lk, seq_lens_q=lq)
+    valid = torch.arange(Tq, device="cuda")[None, :] < lq[:, None]
+    ref = ref * valid[:, :, None, None]
+    tol = {torch.float16: 2e-3, torch.bfloat16: 1e-2}[dtype]
+    for _ in range(20):
+        out = m.sigmoid_attention_padded(q, k, v, seq_lens_k=lk, seq_lens_q=lq)
+        assert m.device_status() == 0
+        assert (out.float() - ref).abs().max().item() <= tol
+        assert out[~valid].abs().max().item() == 0

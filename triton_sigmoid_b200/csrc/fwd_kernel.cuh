@@ -75,9 +75,9 @@ constexpr int kFwdLaunchRegs = 80;  // what 768 threads per CTA get each: 65536 
 // Registers per thread after the re-allocation: the role warps, the output warps (a group of four each)
 // and the sigmoid warps.
 template <int D> struct FwdRegs {
-  static constexpr int kRole = 32;
-  static constexpr int kOutput = 32;
-  static constexpr int kSigmoid = 104;
+  static constexpr int kRole = 48;
+  static constexpr int kOutput = 48;
+  static constexpr int kSigmoid = 96;
   static_assert(kFwdSigmoidWarps * 32 * kSigmoid + 128 * kRole + 128 * kOutput <= kFwdThreads * kFwdLaunchRegs,
                 "the re-allocation may not ask for more registers than the CTA holds");
 };
@@ -92,7 +92,10 @@ struct FwdSmem {
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQOff + 2 * kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
-  static constexpr int kBarOff = kVOff + kStages * kTileBytes;
+  // D = 64: staging for a whole item's O (4 output warps x 2 query tiles x 32 rows x 128 bytes); D = 128 has no room
+  static constexpr int kOutOff = kVOff + kStages * kTileBytes;
+  static constexpr int kOutBytes = (D == 64) ? 4 * 2 * 4096 : 0;
+  static constexpr int kBarOff = kOutOff + kOutBytes;
   // barrier slots (8 bytes each)
   static constexpr int kQFull = 0;                    // [2]
   static constexpr int kKFull = kQFull + 2;           // [kStages]
@@ -420,14 +423,78 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const volatile int* rec = item_ring + 16 * islot;
       if (rec[0] < 0) break;
       const FwdItem it = fwd_load_item(rec);
-      uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) +
-                        2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)(it.tq0 + it.q0 + lane_row) * p.o_st);
       if (it.n_max > 0) {
         ok = mbar_wait_warp(bar(L::kOFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 12);
         if (!ok) break;
         ++act;
         tc_fence_after_sync();
       }
+      if constexpr (D == 64) {
+        // The whole item's O goes through shared memory: out of TMEM one row per lane (two 16-column loads in
+        // flight at a time), rounded to 16 bits, into this warp's patches (16-byte chunks swizzled by row, so
+        // neither side has bank conflicts).  The accumulators are handed back as soon as the last load has
+        // landed - the next item's first P V product waits for that - and only then the rows go out to global
+        // memory, eight lanes per 128-byte row, four rows per instruction.
+        uint8_t* stage = smem_gen + L::kOutOff + 8192 * (warp & 3);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if ((s == 0 ? it.n0 : it.n1) > 0) {
+            const bool live = it.q0 + 128 * s + lane_row < it.Lq;  // rows beyond the valid length are written as zeros
+            const uint32_t o_addr = tmem_lane + kColO + D * s;
+            uint8_t* st_row = stage + 4096 * s + lane * 128;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t ra[16], rb[16];
+              tmem_ld16(o_addr + 32 * h, ra);
+              tmem_ld16(o_addr + 32 * h + 16, rb);
+              tmem_ld_wait_for(ra);
+              tmem_ld_wait_for(rb);
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const uint32_t* r = (q4 < 2) ? ra + 8 * q4 : rb + 8 * (q4 - 2);
+                uint4 w;
+                w.x = pack2<kBF16>(__uint_as_float(r[0]), __uint_as_float(r[1]));
+                w.y = pack2<kBF16>(__uint_as_float(r[2]), __uint_as_float(r[3]));
+                w.z = pack2<kBF16>(__uint_as_float(r[4]), __uint_as_float(r[5]));
+                w.w = pack2<kBF16>(__uint_as_float(r[6]), __uint_as_float(r[7]));
+                if (!live) w = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(st_row + (((4 * h + q4) ^ (lane & 7)) << 4)) = w;
+              }
+            }
+          }
+        }
+        if (it.n_max > 0) {
+          // O has left TMEM: the next item's products may overwrite the accumulators
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(L::kOEmpty));
+        }
+        __syncwarp();
+        const int sub_row = lane >> 3, ch = lane & 7;
+        uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) +
+                          2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh +
+                               (int64_t)(it.tq0 + it.q0 + 32 * (warp & 3) + sub_row) * p.o_st) + 16 * ch;
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          const bool has_o = (s == 0 ? it.n0 : it.n1) > 0;  // else the tile is entirely padding: zero rows
+          // this lane's rows of the tile are sub_row, sub_row + 4, ...; row 4 i + sub_row may be written if 4 i < rows_left
+          const int rows_left = it.row_lim - (it.q0 + 128 * s + 32 * (warp & 3) + sub_row);
+          uint8_t* o_ptr = o_base + 2 * (int64_t)(128 * s) * p.o_st;
+          const uint8_t* st_ptr = stage + 4096 * s + sub_row * 128;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint4 w = make_uint4(0, 0, 0, 0);
+            // (4 i + sub_row) & 7 = sub_row for even i, sub_row + 4 for odd i
+            if (has_o) w = *reinterpret_cast<const uint4*>(st_ptr + 512 * i + ((ch ^ ((sub_row + 4 * (i & 1)) & 7)) << 4));
+            if (4 * i < rows_left) *reinterpret_cast<uint4*>(o_ptr) = w;
+            o_ptr += 8 * p.o_st;
+          }
+        }
+        __syncwarp();  // the patches are free again
+      } else {
+      // D = 128: no room for staging; every lane writes its row's columns as they come out of TMEM
+      uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) +
+                        2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)(it.tq0 + it.q0 + lane_row) * p.o_st);
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
         const int row = it.q0 + 128 * s + lane_row;
@@ -467,6 +534,7 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kOEmpty));
+      }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(L::kItemEmpty + islot));
@@ -745,12 +813,23 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           }
         }
       } else {
-        // warps 0-7: jobs of query tile 0, warps 8-15: tile 1; each warp 64 key columns of its jobs
+        // warps 0-7: jobs of query tile 0, warps 8-15: tile 1; each warp 64 key columns of its jobs.
+        // Jobs are ordered by key tile, query tile 0 before 1: (0,0) (1,0) (0,1) (1,1) ... restricted to
+        // j < n_s, and numbered on across items; job n uses score buffer n % kSBufs in phase n / kSBufs.
+        // The two groups run on across items independently of each other, and a barrier wait only knows the
+        // phase's parity, so a group must never ask for a job more than kSBufs positions after the last one
+        // whose barrier it has seen.  Within and between items in which its tile has jobs that holds by
+        // itself (n1 - n0 is 0 or 1, or n1 = 0: at most two foreign jobs in a row).  A group whose tile has
+        // NO job in an item (a query tile beyond the valid length) therefore does not just skip the item: it
+        // watches the barrier of every one of its jobs go by.
         const int s = warp >> 3;
         const int g = (warp >> 2) & 1;
         const int n_mine = s == 0 ? n0 : n1;
-        for (int j = 0; j < n_mine; ++j) {
-          // jobs are ordered by key tile, query tile 0 before 1: (0,0) (1,0) (0,1) (1,1) ...
+        if (n_mine == 0) {
+          for (int n = jobs_base; n < jobs_base + n0 + n1 && ok; ++n)
+            ok = mbar_wait_warp(bar(L::kSFull + n % kSBufs), (uint32_t)(n / kSBufs) & 1u, abort_flag, kSiteBase + 10 + s);
+        }
+        for (int j = 0; j < n_mine && ok; ++j) {
           const int n = jobs_base + (s == 0 ? j + min(j, n1) : j + min(j + 1, n0));
           const int jb = n % kSBufs;
           ok = mbar_wait_warp(bar(L::kSFull + jb), (uint32_t)(n / kSBufs) & 1u, abort_flag, kSiteBase + 10 + s);
