@@ -213,8 +213,9 @@ def timed(fn, steps: int, warmup: int, flush, barrier) -> float:
 
 def e2e_step_factory(w, fns, q, k, v, do, lens):
     """Step with pinned host inputs/outputs, what a caller whose tensors live on the host would do: per batch
-    element, H2D of q,k,v,dO on a copy stream, forward+backward on the compute stream, D2H of O,dQ,dK,dV on
-    a third stream, chained by events, so uploads, computation and downloads of neighbouring elements overlap.
+    element, H2D of q,k,v and then dO on a copy stream, forward and backward on the compute stream (the forward
+    starts when q,k,v have arrived), D2H of O (during the backward) and of dQ,dK,dV on a third stream, chained
+    by events, so uploads, computation and downloads of neighbouring elements overlap.
     Returns (step, bytes in, bytes out); `step` leaves the current stream waiting for every download."""
     host_in = [t.detach().cpu().pin_memory() for t in (q, k, v, do)]
     host_out = [torch.empty_like(t).pin_memory() for t in host_in]
@@ -232,13 +233,16 @@ def e2e_step_factory(w, fns, q, k, v, do, lens):
         staged = []
         for b in range(B):
             with torch.cuda.stream(s_in):
-                xs = [t[b:b + 1].to(dev, non_blocking=True) for t in host_in]
-                ev = torch.cuda.Event()
-                ev.record(s_in)
-            staged.append((xs, ev))
-        for b, (xs, ev) in enumerate(staged):
-            main.wait_event(ev)
-            qb, kb, vb, dob = xs
+                xs = [t[b:b + 1].to(dev, non_blocking=True) for t in host_in[:3]]
+                ev_qkv = torch.cuda.Event()
+                ev_qkv.record(s_in)  # the forward needs q, k, v only
+                dob = host_in[3][b:b + 1].to(dev, non_blocking=True)
+                ev_do = torch.cuda.Event()
+                ev_do.record(s_in)
+            staged.append((xs, dob, ev_qkv, ev_do))
+        for b, (xs, dob, ev_qkv, ev_do) in enumerate(staged):
+            main.wait_event(ev_qkv)
+            qb, kb, vb = xs
             for t in xs:
                 t.record_stream(main)
             qb.requires_grad_(), kb.requires_grad_(), vb.requires_grad_()
@@ -247,13 +251,21 @@ def e2e_step_factory(w, fns, q, k, v, do, lens):
                 o = padded(qb, kb, vb, seq_lens_k=lb, seq_lens_q=lb, is_causal=w["causal"])
             else:
                 o = dense(qb, kb, vb, is_causal=w["causal"])
+            fwd_done = torch.cuda.Event()
+            fwd_done.record(main)
+            with torch.cuda.stream(s_out):  # O goes home while the backward runs
+                s_out.wait_event(fwd_done)
+                od = o.detach()
+                od.record_stream(s_out)
+                host_out[0][b:b + 1].copy_(od, non_blocking=True)
+            main.wait_event(ev_do)
+            dob.record_stream(main)
             o.backward(dob)
             done = torch.cuda.Event()
             done.record(main)
-            outs = (o.detach(), qb.grad, kb.grad, vb.grad)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(done)
-                for dst, src in zip(host_out, outs):
+                for dst, src in zip(host_out[1:], (qb.grad, kb.grad, vb.grad)):
                     src.record_stream(s_out)
                     dst[b:b + 1].copy_(src, non_blocking=True)
         main.wait_stream(s_out)
@@ -468,7 +480,7 @@ def main():
     ms_e2e = d.max(timed(e2e_fn, e2e_steps, 3, flush, d.barrier)) / e2e_steps
     e2e = {"value": 3.5 * F_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": bi,
            "d2h_bytes_per_step": bo, "ms_per_step": ms_e2e,
-           "how": "pinned host tensors; per batch element H2D, forward+backward, D2H on three streams",
+           "how": "pinned host tensors; per batch element H2D (q,k,v, then dO), forward, backward, D2H (O during the backward, then the gradients) on three streams",
            # what the host link alone allows: both directions at once, nothing else in the step
            "pcie_bound_ms_at_50GBs": max(bi, bo) / 50e9 * 1e3}
 

@@ -62,6 +62,11 @@ enum SigAttnFlags {
    * The split needs no workspace, uses no atomics and is run-to-run deterministic; the fused kernel was
    * measured faster and is therefore the default. */
   SIGATTN_BWD_SPLIT = 1u << 2,
+  /* The default bias of the padded and packed entry points, computed on the device: bias of batch element b
+   * = -log(number of valid keys of b) (the reference's sigmoid_triton_padded.py:995-998, which does it with a
+   * few small tensor kernels before the launch); `bias` and `bias_scalar` are ignored.  An element without
+   * keys gets +inf, where every probability is masked anyway. */
+  SIGATTN_BIAS_NEG_LOG_LK = 1u << 3,
 };
 
 enum SigAttnQuery {

@@ -171,3 +171,28 @@ def test_query_tile_without_work_for_many_items(D, dtype):
         assert m.device_status() == 0
         assert (out.float() - ref).abs().max().item() <= tol
         assert out[~valid].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_default_bias_computed_on_the_device_matches_the_bias_tensor(dtype):
+    """The eager padded call lets the kernels compute the default bias -log(valid keys) (C-ABI flag
+    SIGATTN_BIAS_NEG_LOG_LK); the registered op gets it as a [B] tensor computed by torch, as the reference
+    does (sigmoid_triton_padded.py:995-998).  Same results up to the last bit of the logarithm, also for an
+    element without keys, lengths beyond the tensor and the split backward's kernels."""
+    from triton_sigmoid_b200 import ops
+
+    B, T, H, D = 5, 300, 2, 64
+    q, k, v, do = make_inputs(B, T, T, H, D, dtype, std=0.5, seed=9, requires_grad=True)
+    lens = torch.tensor([300, 0, 17, 129, 400], dtype=torch.int32, device="cuda")
+    scale = 1.0 / D ** 0.5
+    out = m.sigmoid_attention_padded(q, k, v, seq_lens_k=lens, seq_lens_q=lens, is_causal=True)
+    out.backward(do)
+    bias = -torch.log(lens.clamp(min=0, max=T).float())
+    ref_o = ops.sigmoid_attn_padded_fwd_op(q.detach(), k.detach(), v.detach(), lens, lens, bias, None, scale, True)
+    ref_g = ops.sigmoid_attn_padded_bwd_op(q.detach(), k.detach(), v.detach(), do, lens, lens, bias, None, scale, True)
+    tol = 1e-6 if dtype == torch.float32 else 2e-3
+    assert torch.isfinite(out).all()
+    assert (out.detach().float() - ref_o.float()).abs().max().item() <= tol
+    for g, r in zip((q.grad, k.grad, v.grad), ref_g):
+        assert torch.isfinite(g).all()
+        assert (g.float() - r.float()).abs().max().item() <= tol * max(1.0, r.float().abs().max().item())

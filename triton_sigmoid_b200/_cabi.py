@@ -18,6 +18,7 @@ SIGATTN_FP32 = 2
 SIGATTN_CAUSAL = 1
 SIGATTN_ACCURATE = 2
 SIGATTN_BWD_SPLIT = 4
+SIGATTN_BIAS_NEG_LOG_LK = 8
 SIGATTN_STATIC_SCRATCH_ELEMS = 8 * 1024 * 1024
 
 Q_ABI_VERSION, Q_SM_ARCH, Q_MAX_HEAD_DIM, Q_PARAMS_SIZE = 0, 1, 2, 3

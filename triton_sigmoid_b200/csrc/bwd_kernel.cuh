@@ -399,7 +399,7 @@ __device__ __forceinline__ BwdItem bwd_decode_item(const BwdParams& p, int item)
   it.n_q = (it.kv0 < it.Lk) ? max(i_end - it.i_begin, 0) : 0;
   it.ragged_kv = it.kv0 + kBwdTileKV > it.Lk;
   it.ragged_last_q = (it.i_begin + it.n_q) * kBwdTileQ > it.Lq;  // only the last query tile can straddle Lq
-  it.bias = p.bias ? p.bias[it.b] : p.bias_scalar;
+  it.bias = item_bias(p.bias, p.bias_scalar, it.b, it.Lk);
   return it;
 }
 

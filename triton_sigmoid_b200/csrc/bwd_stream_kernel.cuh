@@ -507,7 +507,7 @@ sigattn_bwd_stream_kernel(const __grid_constant__ CUtensorMap r1_map, const __gr
       const BsItem it = bs_decode_item<kDKV>(p, item);
       const int row = it.r0 + lane_row;  // index within the sequence
       if (it.n_jobs > 0) {
-        float c0 = p.bias ? p.bias[it.b] : p.bias_scalar;
+        float c0 = item_bias(p.bias, p.bias_scalar, it.b, kDKV ? it.Lr : it.Lc);
         const float* mod_cols = nullptr;
         if (p.score_mod) {
           const float* mod = p.score_mod + (p.cu_r ? (int64_t)it.tk0 : (int64_t)it.b * p.Tk);

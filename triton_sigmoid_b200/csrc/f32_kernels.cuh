@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(kF32Threads) sigattn_fwd_f32_kernel(const F32P
   const float* qb = p.q + (int64_t)it.bc * p.q_sb + (int64_t)it.h * p.q_sh + (int64_t)it.tq0 * p.q_st;
   const float* kb = p.k + (int64_t)it.bc * p.k_sb + (int64_t)it.h * p.k_sh + (int64_t)it.tk0 * p.k_st;
   const float* vb = p.v + (int64_t)it.bc * p.v_sb + (int64_t)it.h * p.v_sh + (int64_t)it.tk0 * p.v_st;
-  const float bias = p.bias ? p.bias[it.b] : p.bias_scalar;
+  const float bias = item_bias(p.bias, p.bias_scalar, it.b, it.Lk);
   const float* sm = p.score_mod ? p.score_mod + it.sm_off : nullptr;
 
   float o[4][D / 16];
@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(kF32Threads) sigattn_bwd_dkdv_f32_kernel(const
   const float* kb = p.k + (int64_t)it.bc * p.k_sb + (int64_t)it.h * p.k_sh + (int64_t)it.tk0 * p.k_st;
   const float* vb = p.v + (int64_t)it.bc * p.v_sb + (int64_t)it.h * p.v_sh + (int64_t)it.tk0 * p.v_st;
   const float* dob = p.dout + (int64_t)it.bc * p.do_sb + (int64_t)it.h * p.do_sh + (int64_t)it.tq0 * p.do_st;
-  const float bias = p.bias ? p.bias[it.b] : p.bias_scalar;
+  const float bias = item_bias(p.bias, p.bias_scalar, it.b, it.Lk);
   const float* sm = p.score_mod ? p.score_mod + it.sm_off : nullptr;
 
   float dk[4][D / 16], dv[4][D / 16];
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(kF32Threads) sigattn_bwd_dq_f32_kernel(const F
   const float* kb = p.k + (int64_t)it.bc * p.k_sb + (int64_t)it.h * p.k_sh + (int64_t)it.tk0 * p.k_st;
   const float* vb = p.v + (int64_t)it.bc * p.v_sb + (int64_t)it.h * p.v_sh + (int64_t)it.tk0 * p.v_st;
   const float* dob = p.dout + (int64_t)it.bc * p.do_sb + (int64_t)it.h * p.do_sh + (int64_t)it.tq0 * p.do_st;
-  const float bias = p.bias ? p.bias[it.b] : p.bias_scalar;
+  const float bias = item_bias(p.bias, p.bias_scalar, it.b, it.Lk);
   const float* sm = p.score_mod ? p.score_mod + it.sm_off : nullptr;
 
   float dq[4][D / 16];

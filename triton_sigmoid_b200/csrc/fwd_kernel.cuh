@@ -314,7 +314,7 @@ __device__ __forceinline__ FwdItem fwd_decode_item(const FwdParams& p, int item)
   it.n0 = n_kv[0];
   it.n1 = n_kv[1];
   it.n_max = max(it.n0, it.n1);
-  it.bias = p.bias ? p.bias[it.b] : p.bias_scalar;
+  it.bias = item_bias(p.bias, p.bias_scalar, it.b, it.Lk);
   return it;
 }
 

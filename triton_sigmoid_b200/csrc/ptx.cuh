@@ -303,6 +303,14 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[16]) { tme
 __device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
 __device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[8]) { tmem_st8(taddr, r); }
 
+// Additive bias of a work item's batch element: per-element array, or one value for the call, or - when that
+// value is NaN, which is how the host passes SIGATTN_BIAS_NEG_LOG_LK on - minus the logarithm of the
+// element's number of valid keys (+inf for none: every probability is masked there anyway).
+__device__ __forceinline__ float item_bias(const float* bias, float bias_scalar, int b, int n_keys) {
+  if (bias) return bias[b];
+  return (bias_scalar != bias_scalar) ? -logf((float)n_keys) : bias_scalar;
+}
+
 // ---------------------------------------------------------------- math
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;

@@ -318,6 +318,7 @@ int launch_fwd(const SigAttnParams* p, const CUtensorMap& qm, const CUtensorMap&
   fp.score_mod = p->score_mod;
   fp.scale = p->scale;
   fp.bias_scalar = p->bias_scalar;
+  if (p->flags & SIGATTN_BIAS_NEG_LOG_LK) { fp.bias = nullptr; fp.bias_scalar = nanf(""); }  // see item_bias()
   fp.B = p->B;
   fp.H = p->H;
   fp.Tq = p->Tq;
@@ -370,6 +371,7 @@ int launch_bwd_fused(const SigAttnParams* p, const CUtensorMap& qm, const CUtens
   bp.score_mod = p->score_mod;
   bp.scale = p->scale;
   bp.bias_scalar = p->bias_scalar;
+  if (p->flags & SIGATTN_BIAS_NEG_LOG_LK) { bp.bias = nullptr; bp.bias_scalar = nanf(""); }  // see item_bias()
   bp.B = p->B; bp.H = p->H; bp.Tq = p->Tq; bp.Tk = p->Tk;
   bp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
   bp.n_kvblk = (p->Tk + kBwdTileKV - 1) / kBwdTileKV;
@@ -437,6 +439,7 @@ int launch_bwd_stream_mode(const SigAttnParams* p, const CUtensorMap& r1, const 
   bp.score_mod = p->score_mod;
   bp.scale = p->scale;
   bp.bias_scalar = p->bias_scalar;
+  if (p->flags & SIGATTN_BIAS_NEG_LOG_LK) { bp.bias = nullptr; bp.bias_scalar = nanf(""); }  // see item_bias()
   bp.B = p->B; bp.H = p->H; bp.Tk = p->Tk;
   bp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
   bp.n_rblk = (bp.Tr + kBsTile - 1) / kBsTile;
@@ -522,6 +525,7 @@ int launch_f32_d(const SigAttnParams* p, bool backward) {
   fp.score_mod = p->score_mod;
   fp.scale = p->scale;
   fp.bias_scalar = p->bias_scalar;
+  if (p->flags & SIGATTN_BIAS_NEG_LOG_LK) { fp.bias = nullptr; fp.bias_scalar = nanf(""); }  // see item_bias()
   fp.B = p->B; fp.H = p->H; fp.Tq = p->Tq; fp.Tk = p->Tk;
   fp.causal = (p->flags & SIGATTN_CAUSAL) ? 1 : 0;
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);

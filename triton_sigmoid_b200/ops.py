@@ -146,6 +146,9 @@ def _base_params(q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_cau
     p.seq_lens_k = seq_lens_k.data_ptr() if seq_lens_k is not None else None
     if isinstance(bias, torch.Tensor):  # one value per batch element
         p.bias, p.bias_scalar = bias.data_ptr(), 0.0
+    elif bias is None:                  # the padded default, -log(valid keys), computed by the kernels
+        p.bias, p.bias_scalar = None, 0.0
+        p.flags |= _cabi.SIGATTN_BIAS_NEG_LOG_LK
     else:                               # one value for the whole call: no device tensor needed
         p.bias, p.bias_scalar = None, float(bias)
     p.score_mod = score_mod.data_ptr() if score_mod is not None else None
@@ -302,8 +305,9 @@ class _EagerSigmoidAttention(torch.autograd.Function):
     library through this plain autograd function, because a `torch.library.custom_op` round trip with its
     generated autograd wrapper costs about 100 us of host time per forward + backward pair, which is more
     than the kernels of a short-sequence call take.  Under `torch.compile` the public functions use the
-    registered ops (fake kernels, autograd registration) instead.  `bias` is a [B] tensor or a Python
-    float (one value for the whole call, passed by value)."""
+    registered ops (fake kernels, autograd registration) instead.  `bias` is a [B] tensor, a Python float
+    (one value for the whole call, passed by value) or None (minus the logarithm of each batch element's
+    number of valid keys, computed by the kernels)."""
 
     @staticmethod
     def forward(ctx, q, k, v, bias, score_mod, seq_lens_q, seq_lens_k, scale, is_causal):
@@ -582,9 +586,11 @@ def sigmoid_attention_padded(
         bias = float(sigmoid_bias)
     elif full_k:
         bias = -math.log(float(T_k)) if T_k > 0 else float("inf")
-    else:
+    elif compiling:
         # -log(0) = +inf for an empty key set; every probability is masked there anyway
         bias = -torch.log(seq_lens_k.clamp(min=0, max=T_k).float())
+    else:
+        bias = None  # the same value, computed by the kernels from the lengths they clamp anyway
 
     if compiling:
         for x in (query, key, value):
