@@ -423,6 +423,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-breakdown", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the extra.workloads record")
+    ap.add_argument("--extra-workloads", default=None,
+                    help="comma-separated workload names for the extra.workloads record instead of the default list "
+                         "(e.g. a sequence-length sweep: sweep:512:64:bf16:dense:full,sweep:2048:64:bf16:dense:full)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -545,7 +548,7 @@ def main():
     torch.cuda.empty_cache()
     if not args.no_extra:
         extra = {}
-        for name in EXTRA_WORKLOADS:
+        for name in (args.extra_workloads.split(",") if args.extra_workloads else EXTRA_WORKLOADS):
             if name == w["name"]:
                 continue
             try:
