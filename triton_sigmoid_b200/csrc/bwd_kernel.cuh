@@ -800,7 +800,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         if (!ok) break;
         tc_fence_after_sync();
         if constexpr (kTwoS) {
-          // dQ first: the group that owns the tile waits for it before it can move on
+          // dQ first: the compute warps wait for it before they rewrite the shared-memory copy of dS, its
+          // drain starts earlier, and at the last tile of an item it is complete before dK is, so that the
+          // epilogue may use the dS buffer as scratch as soon as dK_j, dV_j are complete
 #pragma unroll
           for (int kk = 0; kk < kBwdTileKV / 16; ++kk) {
             const uint64_t kd = make_desc(k_lo + kv_off + kk * (2048 >> 4), hi), dsd = make_desc(ds_lo + kk * (2048 >> 4), hi);
@@ -858,13 +860,12 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       if (item < 0) break;
       const int b = it.b, h = it.h, kv0 = it.kv0, Lq = it.Lq, Lk = it.Lk, i_begin = it.i_begin, n_q = it.n_q;
       const int kv = kv0 + lane_row;
-      // row 0 of this sequence's dK / dV
-      uint8_t* dk_base = reinterpret_cast<uint8_t*>(p.dk) +
-                         2 * ((int64_t)it.bc * p.dk_sb + (int64_t)h * p.dk_sh + (int64_t)it.tk0 * p.dk_st);
-      uint8_t* dv_base = reinterpret_cast<uint8_t*>(p.dv) +
-                         2 * ((int64_t)it.bc * p.dv_sb + (int64_t)h * p.dv_sh + (int64_t)it.tk0 * p.dv_st);
       if (n_q == 0) {
         // no query sees this key tile: its gradients are zero
+        uint8_t* dk_base = reinterpret_cast<uint8_t*>(p.dk) +
+                           2 * ((int64_t)it.bc * p.dk_sb + (int64_t)h * p.dk_sh + (int64_t)it.tk0 * p.dk_st);
+        uint8_t* dv_base = reinterpret_cast<uint8_t*>(p.dv) +
+                           2 * ((int64_t)it.bc * p.dv_sb + (int64_t)h * p.dv_sh + (int64_t)it.tk0 * p.dv_st);
         constexpr int kChunksPerRow = D * 2 / 16;
         for (int i = threadIdx.x; i < kBwdTileKV * kChunksPerRow; i += kBwdComputeWarps * 32) {
           const int row = kv0 + i / kChunksPerRow;
@@ -992,12 +993,39 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
-        if (kv < it.key_lim) {
-          uint8_t* out_row = (is_dk ? dk_base + 2 * (int64_t)kv * p.dk_st : dv_base + 2 * (int64_t)kv * p.dv_st) + 2 * col0;
+        // row 0 of this sequence's dK or dV, at this warp's columns
+        const int64_t out_st = is_dk ? p.dk_st : p.dv_st;
+        uint8_t* out_base = is_dk ? reinterpret_cast<uint8_t*>(p.dk) + 2 * ((int64_t)it.bc * p.dk_sb + (int64_t)h * p.dk_sh + (int64_t)it.tk0 * p.dk_st)
+                                  : reinterpret_cast<uint8_t*>(p.dv) + 2 * ((int64_t)it.bc * p.dv_sb + (int64_t)h * p.dv_sh + (int64_t)it.tk0 * p.dv_st);
+        out_base += 2 * col0;
+        if constexpr (D == 64) {
+          // A lane holds 64 bytes of its key row; written as they are, one store instruction would touch 32
+          // lines (the load/store unit takes them one at a time: about 2000 clocks per item for the CTA).
+          // Each warp therefore turns its 32 x 64-byte block through its own part of the shared-memory copy
+          // of dS - the rows and 16-byte slots it writes in phase B, which no product reads any more once
+          // the item's last dK is complete - so that four lanes cover a row and an instruction 8 rows.
+          uint8_t* ds_gen = smem_gen + L::kDsOff + (cg >> 1) * 16384 + quarter * 32 * 128;  // row 0 of this warp's quarter
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c) {
+          for (int q4 = 0; q4 < 4; ++q4)
+            *reinterpret_cast<uint4*>(ds_gen + lane * 128 + (((chunk0 + q4) ^ sw) << 4)) = w[0][q4];
+          __syncwarp();
+          const int c = lane & 3;
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(out_row + 64 * c + 16 * q4) = w[c][q4];
+          for (int i = 0; i < 4; ++i) {
+            const int r = 8 * i + (lane >> 2);  // row within the quarter (quarter * 32 is a multiple of 8: same swizzle phase)
+            const uint4 x = *reinterpret_cast<const uint4*>(ds_gen + r * 128 + (((chunk0 + c) ^ (uint32_t)(r & 7)) << 4));
+            const int krow = kv0 + quarter * 32 + r;
+            if (krow < it.key_lim) *reinterpret_cast<uint4*>(out_base + 2 * (int64_t)krow * out_st + 16 * c) = x;
+          }
+          __syncwarp();  // phase B of the next item rewrites these slots
+        } else {
+          if (kv < it.key_lim) {
+            uint8_t* out_row = out_base + 2 * (int64_t)kv * out_st;
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(out_row + 64 * c + 16 * q4) = w[c][q4];
+            }
           }
         }
       }
