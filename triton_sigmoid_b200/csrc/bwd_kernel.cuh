@@ -42,6 +42,7 @@
 //               stood idle and the next tile's scores, which reuse the dQ columns, were late.  Eight
 //               warps that do nothing else take dQ out of TMEM as soon as it is complete (freeing the
 //               columns at once) and feed the reductions while the compute warps are two phases ahead.
+//               They also take the epilogue (dK_j, dV_j) of short items, see kDrainEpilogueMaxTiles.
 //               Registers are re-balanced with setmaxnreg (compute 80, role warps 72, drain warps 56 per thread);
 //               to fit, the compute warps do not keep P in registers between their two phases but read its
 //               16-bit copy back from TMEM.
@@ -89,7 +90,12 @@ constexpr int kBwdComputeWarps = 16;
 constexpr int kBwdProducerWarp = 16;
 constexpr int kBwdIssuerA = 17;
 constexpr int kBwdIssuerB = 18;
-constexpr int kBwdDrainWarps = 8;    // D = 64 only
+constexpr int kBwdDrainWarps = 8;
+// D = 64: the drain warps also take the epilogue (dK_j, dV_j out of TMEM and to global memory) of items with at most
+// this many query tiles, so that the compute warps go straight on to the next item; for longer items, whose
+// epilogue is a small share, the compute warps do it themselves (the drain warps, busy with it, would fall
+// behind with the next item's dQ tiles: measured -1.5 % at 32 tiles per item, +7 % at 4).
+constexpr int kDrainEpilogueMaxTiles = 8;    // D = 64 only
 constexpr int kBwdFirstDrainWarp = 20;
 template <int D> constexpr int kBwdThreads = (D == 64) ? (kBwdFirstDrainWarp + kBwdDrainWarps) * 32 : 20 * 32;
 constexpr int kBwdTileKV = 128;
@@ -132,7 +138,7 @@ struct BwdSmem {
   static constexpr int kKvFix = kDkvFull + 1;         // [2] per K/V buffer: padded rows of K_j zeroed
   static constexpr int kQdoFix = kKvFix + 2;          // [2] per stage: padded rows of the last Q_i / dO_i zeroed
   static constexpr int kKvEmpty = kQdoFix + 2;        // [2] per K/V buffer, both issuers: every product that reads it is complete
-  static constexpr int kDkvEmpty = kKvEmpty + 2;      // dK_j, dV_j read out of TMEM (16 warps)
+  static constexpr int kDkvEmpty = kKvEmpty + 2;      // dK_j, dV_j read out of TMEM (every compute and drain warp arrives, see kDrainEpilogueMaxTiles)
   static constexpr int kItemFull = kDkvEmpty + 1;     // [2] item index published
   static constexpr int kItemEmpty = kItemFull + 2;    // [2] item index read by every consumer warp
   static constexpr int kNumBars = kItemEmpty + 2;
@@ -478,7 +484,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     mbar_init(bar(L::kDqEmpty + 0), kDrainWarps ? kBwdDrainWarps : kBwdComputeWarps);
     mbar_init(bar(L::kDqEmpty + 1), kDrainWarps ? kBwdDrainWarps : kBwdComputeWarps);
     mbar_init(bar(L::kDkvFull), 1);
-    mbar_init(bar(L::kDkvEmpty), kBwdComputeWarps);
+    mbar_init(bar(L::kDkvEmpty), kBwdComputeWarps + (kDrainWarps ? kBwdDrainWarps : 0));
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(L::kItemFull + i), 1);
       mbar_init(bar(L::kItemEmpty + i), kItemReaders);
@@ -532,6 +538,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
       uint8_t* patch = smem_gen + L::kDqPatchOff + dw * L::kDqPatchBytes;
       int g = 0;
+      int act = 0;  // items with work so far
       bool ok = true;
       for (int k = 0; ok; ++k) {
         BwdItem it;
@@ -572,7 +579,66 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
           }
           __syncwarp();  // the patch is rewritten at the next tile
         }
+        if (!ok) break;
         g += it.n_q;
+
+        // ---- epilogue of the item: dV_j, then dK_j, out of TMEM, rounded, through the patch (so that four
+        // lanes cover a row's 64 bytes and an instruction 8 rows; a lane writing its own row would touch 32
+        // lines per instruction, which the load/store unit takes one at a time) and out to global memory,
+        // while the compute warps are already on the next item's first tiles.
+        if (it.n_q > kDrainEpilogueMaxTiles) {
+          // the compute warps' business; nothing of the accumulators is needed here
+          ++act;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
+          continue;
+        }
+        ok = mbar_wait_warp(bar(L::kDkvFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 15);
+        if (!ok) break;
+        ++act;
+        tc_fence_after_sync();
+        const bool row_ok = it.kv0 + quarter * 32 + lane < it.Lk;  // padded key rows get zero gradients
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
+          const uint32_t acc_addr = tmem + lane_addr + (which ? kColDk : kColDv) + 32u * (uint32_t)half;
+          const float mul = which ? p.scale : 1.0f;
+          uint4* mine = reinterpret_cast<uint4*>(patch + lane * L::kDqPatchRow);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            uint32_t r[16];
+            tmem_ld(acc_addr + 16 * u, r);
+            tmem_ld_wait_for(r);
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+              uint4 w;
+              w.x = pack2<kBF16>(mul * __uint_as_float(r[8 * m + 0]), mul * __uint_as_float(r[8 * m + 1]));
+              w.y = pack2<kBF16>(mul * __uint_as_float(r[8 * m + 2]), mul * __uint_as_float(r[8 * m + 3]));
+              w.z = pack2<kBF16>(mul * __uint_as_float(r[8 * m + 4]), mul * __uint_as_float(r[8 * m + 5]));
+              w.w = pack2<kBF16>(mul * __uint_as_float(r[8 * m + 6]), mul * __uint_as_float(r[8 * m + 7]));
+              if (!row_ok) w = make_uint4(0, 0, 0, 0);
+              mine[2 * u + m] = w;
+            }
+          }
+          if (which == 1) {
+            // both accumulators are out of TMEM: the next item's first dV / dK products may overwrite them
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
+          }
+          __syncwarp();
+          const int64_t out_st = which ? p.dk_st : p.dv_st;
+          uint8_t* out = which ? reinterpret_cast<uint8_t*>(p.dk) + 2 * ((int64_t)it.bc * p.dk_sb + (int64_t)it.h * p.dk_sh + (int64_t)it.tk0 * p.dk_st)
+                               : reinterpret_cast<uint8_t*>(p.dv) + 2 * ((int64_t)it.bc * p.dv_sb + (int64_t)it.h * p.dv_sh + (int64_t)it.tk0 * p.dv_st);
+          out += 64 * half + 16 * (lane & 3);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r8 = 8 * i + (lane >> 2);
+            const uint4 x = *reinterpret_cast<const uint4*>(patch + r8 * L::kDqPatchRow + 16 * (lane & 3));
+            const int krow = it.kv0 + quarter * 32 + r8;
+            if (krow < it.key_lim) *reinterpret_cast<uint4*>(out + 2 * (int64_t)krow * out_st) = x;
+          }
+          __syncwarp();  // the patch is rewritten by the next pass / the next item's first dQ tile
+        }
       }
     }
   } else
@@ -964,8 +1030,13 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       if (!ok) break;
 
       // ------------------------------------------------------------ epilogue of the item
-      // (before the drain of the last dQ tile, whose product is still running)
+      // (before the drain of the last dQ tile, whose product is still running); short items' at D = 64 is the
+      // drain warps' (kDrainEpilogueMaxTiles): nothing of the accumulators is needed here then
       // column groups 0,1 store dV, groups 2,3 store dK (each half of the head dimension)
+      if (kDrainWarps && n_q <= kDrainEpilogueMaxTiles) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
+      } else {
       ok = mbar_wait_warp(bar(L::kDkvFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 15);
       if (!ok) break;
       {
@@ -1028,6 +1099,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
             }
           }
         }
+      }
       }
       if constexpr (!kDrainWarps) {
         drain_dq(n_q - 1);
