@@ -274,6 +274,43 @@ def e2e_step_factory(w, fns, q, k, v, do, lens):
     return step, nbytes, nbytes
 
 
+def host_link_probe(device, nbytes: int = 64 << 20) -> dict:
+    """What this box's host link gives: 64 MiB pinned copies host-to-device, device-to-host and both at once
+    (CUDA events, best of three).  The end-to-end step streams in both directions at the same time, so a box on
+    which the two directions do not overlap (both-at-once close to the sum of the two) shows in `e2e` directly."""
+    h_in = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    h_out = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d_in = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    d_out = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    s1, s2 = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def run(up: bool, down: bool) -> float:
+        best = float("inf")
+        for _ in range(4):
+            torch.cuda.synchronize(device)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            main = torch.cuda.current_stream(device)
+            a.record(main)
+            s1.wait_event(a)
+            s2.wait_event(a)
+            if up:
+                with torch.cuda.stream(s1):
+                    d_in.copy_(h_in, non_blocking=True)
+            if down:
+                with torch.cuda.stream(s2):
+                    h_out.copy_(d_out, non_blocking=True)
+            main.wait_stream(s1)
+            main.wait_stream(s2)
+            b.record(main)
+            torch.cuda.synchronize(device)
+            best = min(best, a.elapsed_time(b))
+        return best
+
+    up, down, both = run(True, False), run(False, True), run(True, True)
+    return {"h2d_gbs": nbytes / up / 1e6, "d2h_gbs": nbytes / down / 1e6, "both_at_once_ms": both,
+            "one_direction_ms": max(up, down), "mib": nbytes >> 20}
+
+
 # ----------------------------------------------------------------------------- CPU baseline
 def cpu_baseline(w: dict, budget_s: float = 20.0) -> dict:
     """Reference's own PyTorch CPU code (fp32, autograd) on a bounded sample of the workload:
@@ -486,6 +523,8 @@ def main():
            "how": "pinned host tensors; per batch element H2D (q,k,v, then dO), forward, backward, D2H (O during the backward, then the gradients) on three streams",
            # what the host link alone allows: both directions at once, nothing else in the step
            "pcie_bound_ms_at_50GBs": max(bi, bo) / 50e9 * 1e3}
+    if rank == 0:
+        e2e["host_link_probe"] = host_link_probe(device)
 
     breakdown = {}
     if not args.no_breakdown:
