@@ -26,7 +26,9 @@
 //   warps 20-23  output warps (one per TMEM lane quarter): wait for an item's last P V product, read O out of
 //                TMEM, round it and write it to global memory, while the sigmoid warps are already at work
 //                on the next item's scores (measured against the sigmoid warps writing O themselves:
-//                +8 % at N = 512, +3 % at N = 1024-2048, +1 % at N = 4096)
+//                +8 % at N = 512, +3 % at N = 1024-2048, +1 % at N = 4096); O goes through shared memory
+//                so that whole rows leave per instruction (D = 64: the item's two tiles at once, D = 128:
+//                one tile at a time)
 // There is no row normaliser in sigmoid attention, so O simply accumulates in TMEM over the
 // whole key loop of an item.  The (query tile, key tile) jobs are processed in a fixed order through a
 // small ring of S buffers in TMEM (3 when D = 64, 2 when D = 128): the issuer computes the
@@ -92,9 +94,10 @@ struct FwdSmem {
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQOff + 2 * kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
-  // D = 64: staging for a whole item's O (4 output warps x 2 query tiles x 32 rows x 128 bytes); D = 128 has no room
+  // staging for the output warps, 8 KB each: D = 64 a whole item's O (2 query tiles x 32 rows x 128 bytes),
+  // D = 128 one query tile at a time (32 rows x 256 bytes)
   static constexpr int kOutOff = kVOff + kStages * kTileBytes;
-  static constexpr int kOutBytes = (D == 64) ? 4 * 2 * 4096 : 0;
+  static constexpr int kOutBytes = 4 * 8192;
   static constexpr int kBarOff = kOutOff + kOutBytes;
   // barrier slots (8 bytes each)
   static constexpr int kQFull = 0;                    // [2]
@@ -492,48 +495,64 @@ sigattn_fwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         }
         __syncwarp();  // the patches are free again
       } else {
-      // D = 128: no room for staging; every lane writes its row's columns as they come out of TMEM
+      // D = 128: room to stage one query tile at a time (32 rows x 256 bytes per warp).  Tile 0 goes through the
+      // patch and out, then tile 1; the accumulators are handed back after the last TMEM load.  Rows leave
+      // with sixteen lanes per 256-byte row; a lane writing its own row's columns as they come out of TMEM
+      // touched 32 lines per store instruction, which the load/store unit takes one at a time (about 4000
+      // clocks per item) and which held the hand-back up, since the loads were interleaved with those stores.
+      uint8_t* stage = smem_gen + L::kOutOff + 8192 * (warp & 3);
       uint8_t* o_base = reinterpret_cast<uint8_t*>(p.o) +
-                        2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh + (int64_t)(it.tq0 + it.q0 + lane_row) * p.o_st);
-#pragma unroll
+                        2 * ((int64_t)it.bc * p.o_sb + (int64_t)it.h * p.o_sh +
+                             (int64_t)(it.tq0 + it.q0 + 32 * (warp & 3) + (lane >> 4)) * p.o_st) + 16 * (lane & 15);
+      const int last_tile = it.n1 > 0 ? 1 : 0;  // the last tile that has accumulators to read (n_max > 0 means n0 > 0 or n1 > 0)
+#pragma unroll 1
       for (int s = 0; s < 2; ++s) {
-        const int row = it.q0 + 128 * s + lane_row;
-        const bool in_rows = row < it.row_lim;  // rows this item may write at all
-        const bool live = row < it.Lq;          // rows beyond the valid length are written as zeros
-        uint8_t* o_row = o_base + 2 * (int64_t)(128 * s) * p.o_st;
-        if ((s == 0 ? it.n0 : it.n1) > 0) {
+        const bool has_o = (s == 0 ? it.n0 : it.n1) > 0;  // else the tile is entirely padding: zero rows
+        if (has_o) {
+          const bool live = it.q0 + 128 * s + lane_row < it.Lq;  // rows beyond the valid length are written as zeros
           const uint32_t o_addr = tmem_lane + kColO + D * s;
+          uint8_t* st_row = stage + lane * 256;
 #pragma unroll
-          for (int c = 0; c < D / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld16(o_addr + 16 * c, r);
-            tmem_ld_wait_for(r);
-            uint4 w0, w1;
-            w0.x = pack2<kBF16>(__uint_as_float(r[0]), __uint_as_float(r[1]));
-            w0.y = pack2<kBF16>(__uint_as_float(r[2]), __uint_as_float(r[3]));
-            w0.z = pack2<kBF16>(__uint_as_float(r[4]), __uint_as_float(r[5]));
-            w0.w = pack2<kBF16>(__uint_as_float(r[6]), __uint_as_float(r[7]));
-            w1.x = pack2<kBF16>(__uint_as_float(r[8]), __uint_as_float(r[9]));
-            w1.y = pack2<kBF16>(__uint_as_float(r[10]), __uint_as_float(r[11]));
-            w1.z = pack2<kBF16>(__uint_as_float(r[12]), __uint_as_float(r[13]));
-            w1.w = pack2<kBF16>(__uint_as_float(r[14]), __uint_as_float(r[15]));
-            if (!live) w0 = w1 = make_uint4(0, 0, 0, 0);
-            if (in_rows) {
-              *reinterpret_cast<uint4*>(o_row + 32 * c) = w0;
-              *reinterpret_cast<uint4*>(o_row + 32 * c + 16) = w1;
+          for (int h = 0; h < 4; ++h) {
+            uint32_t ra[16], rb[16];
+            tmem_ld16(o_addr + 32 * h, ra);
+            tmem_ld16(o_addr + 32 * h + 16, rb);
+            tmem_ld_wait_for(ra);
+            tmem_ld_wait_for(rb);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const uint32_t* r = (q4 < 2) ? ra + 8 * q4 : rb + 8 * (q4 - 2);
+              uint4 w;
+              w.x = pack2<kBF16>(__uint_as_float(r[0]), __uint_as_float(r[1]));
+              w.y = pack2<kBF16>(__uint_as_float(r[2]), __uint_as_float(r[3]));
+              w.z = pack2<kBF16>(__uint_as_float(r[4]), __uint_as_float(r[5]));
+              w.w = pack2<kBF16>(__uint_as_float(r[6]), __uint_as_float(r[7]));
+              if (!live) w = make_uint4(0, 0, 0, 0);
+              // 16-byte chunk 4 h + q4 of the row, its low three bits swizzled by the row
+              *reinterpret_cast<uint4*>(st_row + ((((4 * h + q4) & 8) | (((4 * h + q4) ^ lane) & 7)) << 4)) = w;
             }
           }
-        } else if (in_rows) {
-          // this tile is entirely padding: zero rows
-#pragma unroll
-          for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(o_row + 16 * c) = make_uint4(0, 0, 0, 0);
         }
-      }
-      if (it.n_max > 0) {
-        // O has left TMEM: the next item's products may overwrite the accumulators
-        tc_fence_before_sync();
+        if (it.n_max > 0 && s == last_tile) {
+          // O has left TMEM: the next item's products may overwrite the accumulators
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(L::kOEmpty));
+        }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kOEmpty));
+        // this lane's rows of the tile are (lane >> 4), (lane >> 4) + 2, ...; row 2 i + (lane >> 4) may be written if 2 i < rows_left
+        const int rows_left = it.row_lim - (it.q0 + 128 * s + 32 * (warp & 3) + (lane >> 4));
+        uint8_t* o_ptr = o_base + 2 * (int64_t)(128 * s) * p.o_st;
+        const int ch = lane & 15;
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+          const int r = 2 * i + (lane >> 4);
+          uint4 w = make_uint4(0, 0, 0, 0);
+          if (has_o) w = *reinterpret_cast<const uint4*>(stage + r * 256 + (((ch & 8) | ((ch ^ r) & 7)) << 4));
+          if (2 * i < rows_left) *reinterpret_cast<uint4*>(o_ptr) = w;
+          o_ptr += 4 * p.o_st;
+        }
+        __syncwarp();  // the patch is free again
       }
       }
       __syncwarp();
