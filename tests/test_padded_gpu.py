@@ -196,3 +196,43 @@ def test_default_bias_computed_on_the_device_matches_the_bias_tensor(dtype):
     for g, r in zip((q.grad, k.grad, v.grad), ref_g):
         assert torch.isfinite(g).all()
         assert (g.float() - r.float()).abs().max().item() <= tol * max(1.0, r.float().abs().max().item())
+
+
+def test_backward_repeatable_with_short_and_long_items_mixed():
+    """Cross-attention lengths drawn independently for queries and keys (B=16, T=2048, H=8, D=64): key tiles
+    with a handful of query tiles and with sixteen follow each other on every SM.  In the backward kernel the
+    epilogue of the short ones belongs to the drain warps and that of the long ones to the compute warps, which
+    run ahead of each other; dK and dV are accumulated in a fixed order, so any mix-up in handing the
+    accumulators back shows as a run-to-run difference.  Also compared with fp32 torch math."""
+    B, T, H, D = 16, 2048, 8, 64
+    g = torch.Generator().manual_seed(7)
+    q, k, v, do = make_inputs(B, T, T, H, D, torch.bfloat16, std=0.5, seed=3, requires_grad=True)
+    for trial in range(3):
+        lq = torch.randint(0, T + 1, (B,), generator=g, dtype=torch.int32)
+        lk = torch.randint(0, T + 1, (B,), generator=g, dtype=torch.int32)
+        lq[trial], lq[trial + 3], lq[trial + 6] = 58, 128, 303
+        lq, lk = lq.cuda(), lk.cuda()
+        first = None
+        for rep in range(10):
+            q.grad = k.grad = v.grad = None
+            out = m.sigmoid_attention_padded(q, k, v, seq_lens_k=lk, seq_lens_q=lq)
+            out.backward(do)
+            cur = (out.detach().clone(), k.grad.clone(), v.grad.clone(), q.grad.clone())
+            assert m.device_status() == 0
+            if first is None:
+                first = cur
+            else:
+                for name, a, b in zip(("o", "dk", "dv"), cur, first):
+                    assert torch.equal(a, b), f"{name} differs between runs (trial {trial}, repetition {rep})"
+                assert rel_l2(cur[3], first[3]) <= 1e-4
+        qf, kf, vf = [t.detach().float().requires_grad_() for t in (q, k, v)]
+        vq = torch.arange(T, device="cuda")[None, :] < lq[:, None]
+        vk = torch.arange(T, device="cuda")[None, :] < lk[:, None]
+        ref = m.sigmoid_attention_ref(qf, kf, vf, seq_lens_k=lk, seq_lens_q=lq) * vq[:, :, None, None]
+        ref.backward(do.float() * vq[:, :, None, None])
+        assert (first[0].float() - ref).abs().max().item() <= 1e-2
+        for gr, r, mask in ((first[3], qf.grad, vq), (first[1], kf.grad, vk), (first[2], vf.grad, vk)):
+            assert torch.isfinite(gr).all()
+            assert gr[~mask].abs().max().item() == 0
+            if mask.any() and r[mask].abs().max() > 0:
+                assert rel_l2(gr[mask], r[mask]) <= 1e-2

@@ -138,8 +138,8 @@ struct BwdSmem {
   static constexpr int kKvFix = kDkvFull + 1;         // [2] per K/V buffer: padded rows of K_j zeroed
   static constexpr int kQdoFix = kKvFix + 2;          // [2] per stage: padded rows of the last Q_i / dO_i zeroed
   static constexpr int kKvEmpty = kQdoFix + 2;        // [2] per K/V buffer, both issuers: every product that reads it is complete
-  static constexpr int kDkvEmpty = kKvEmpty + 2;      // dK_j, dV_j read out of TMEM (every compute and drain warp arrives, see kDrainEpilogueMaxTiles)
-  static constexpr int kItemFull = kDkvEmpty + 1;     // [2] item index published
+  static constexpr int kDkvEmpty = kKvEmpty + 2;      // [2] dK_j, dV_j read out of TMEM: [0] by the 16 compute warps, [1] by the 8 drain warps (short items at D = 64)
+  static constexpr int kItemFull = kDkvEmpty + 2;     // [2] item index published
   static constexpr int kItemEmpty = kItemFull + 2;    // [2] item index read by every consumer warp
   static constexpr int kNumBars = kItemEmpty + 2;
   static constexpr int kMiscOff = kBarOff + 8 * kNumBars;  // tmem base (u32), abort flag (int), 2 x item record (16 int each)
@@ -484,7 +484,8 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     mbar_init(bar(L::kDqEmpty + 0), kDrainWarps ? kBwdDrainWarps : kBwdComputeWarps);
     mbar_init(bar(L::kDqEmpty + 1), kDrainWarps ? kBwdDrainWarps : kBwdComputeWarps);
     mbar_init(bar(L::kDkvFull), 1);
-    mbar_init(bar(L::kDkvEmpty), kBwdComputeWarps + (kDrainWarps ? kBwdDrainWarps : 0));
+    mbar_init(bar(L::kDkvEmpty + 0), kBwdComputeWarps);
+    mbar_init(bar(L::kDkvEmpty + 1), kBwdDrainWarps);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(L::kItemFull + i), 1);
       mbar_init(bar(L::kItemEmpty + i), kItemReaders);
@@ -587,10 +588,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         // lines per instruction, which the load/store unit takes one at a time) and out to global memory,
         // while the compute warps are already on the next item's first tiles.
         if (it.n_q > kDrainEpilogueMaxTiles) {
-          // the compute warps' business; nothing of the accumulators is needed here
-          ++act;
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
+          ++act;  // the compute warps' business
           continue;
         }
         ok = mbar_wait_warp(bar(L::kDkvFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 15);
@@ -623,7 +621,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
             // both accumulators are out of TMEM: the next item's first dV / dK products may overwrite them
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
+            if (lane == 0) mbar_arrive(bar(L::kDkvEmpty + 1));
           }
           __syncwarp();
           const int64_t out_st = which ? p.dk_st : p.dv_st;
@@ -839,6 +837,10 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
     };
     int g = 0;    // query tiles issued so far (all items)
     int act = 0;  // items with work so far
+    // who reads the accumulators of an item (0: compute warps, 1: drain warps), for the previous item, and the
+    // parity of each of the two hand-back barriers' next phase
+    int prev_kind = 0;
+    uint32_t empty_par = 0u;  // bit kind
     bool ok = true;
     for (int k = 0; ok; ++k) {
       BwdItem it;
@@ -847,15 +849,23 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       if (it.n_q == 0) continue;
       const int kb = act % L::kKvBufs;
       const uint32_t kv_off = (uint32_t)kb * kStageStep;
-      // the accumulators still hold the previous item's dK, dV until the compute warps have read them
-      if (act > 0) ok = mbar_wait_warp(bar(L::kDkvEmpty), (uint32_t)(act - 1) & 1u, abort_flag, kSiteBase + 33);
+      // the accumulators still hold the previous item's dK, dV until its epilogue has read them
+      if (act > 0) {
+        ok = mbar_wait_warp(bar(L::kDkvEmpty + prev_kind), (empty_par >> prev_kind) & 1u, abort_flag, kSiteBase + 33);
+        empty_par ^= 1u << prev_kind;
+      }
+      prev_kind = (kDrainWarps && it.n_q <= kDrainEpilogueMaxTiles) ? 1 : 0;
       for (int t = 0; t < it.n_q && ok; ++t) {
         const int gt = g + t;
         const int st = gt & 1;
         const uint32_t par = (uint32_t)gt & 1u;
         const uint32_t acc0 = t > 0 ? 1u : 0u;
-        // dV += P^T dO
-        ok = mbar_wait_warp(bar(L::kPReady + sbuf(gt)), spar(gt), abort_flag, kSiteBase + 8);
+        // dV += P^T dO.  The probabilities only prove that Q_i has landed (they come from S^T = K Q^T): this
+        // product is the first of this warp's to read dO_i and waits for that tile itself - without it a row
+        // of the stage could still hold the tile of two steps earlier (seen once in some hundred runs on one
+        // shape, as dV rows carrying dO of query q - 256 instead of q).
+        ok = mbar_wait_warp(bar(L::kDoFull + st), (uint32_t)(gt >> 1) & 1u, abort_flag, kSiteBase + 22);
+        ok = ok && mbar_wait_warp(bar(L::kPReady + sbuf(gt)), spar(gt), abort_flag, kSiteBase + 8);
         if (!ok) break;
         tc_fence_after_sync();
         issue_acc(kColDv, kColS + 128u * (uint32_t)sbuf(gt), do_lo0 + (uint32_t)st * kStageStep, acc0);
@@ -1034,8 +1044,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       // drain warps' (kDrainEpilogueMaxTiles): nothing of the accumulators is needed here then
       // column groups 0,1 store dV, groups 2,3 store dK (each half of the head dimension)
       if (kDrainWarps && n_q <= kDrainEpilogueMaxTiles) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
+        // (no arrival either: each of the two hand-back barriers is arrived on only by the warps that read the
+        // accumulators of that item - a group that runs ahead must not add arrivals to a phase that still
+        // waits for the other group's)
       } else {
       ok = mbar_wait_warp(bar(L::kDkvFull), (uint32_t)act & 1u, abort_flag, kSiteBase + 15);
       if (!ok) break;
@@ -1063,7 +1074,7 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         // the accumulators are in registers: the next item's first dV / dK products may overwrite them
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(L::kDkvEmpty));
+        if (lane == 0) mbar_arrive(bar(L::kDkvEmpty + 0));
         // row 0 of this sequence's dK or dV, at this warp's columns
         const int64_t out_st = is_dk ? p.dk_st : p.dv_st;
         uint8_t* out_base = is_dk ? reinterpret_cast<uint8_t*>(p.dk) + 2 * ((int64_t)it.bc * p.dk_sb + (int64_t)h * p.dk_sh + (int64_t)it.tk0 * p.dk_st)
