@@ -849,8 +849,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
       if (it.n_q == 0) continue;
       const int kb = act % L::kKvBufs;
       const uint32_t kv_off = (uint32_t)kb * kStageStep;
+      ok = mbar_wait_warp(bar(L::kKvFull + kb), (uint32_t)(act / L::kKvBufs) & 1u, abort_flag, kSiteBase + 24);  // K_j for dQ
       // the accumulators still hold the previous item's dK, dV until its epilogue has read them
-      if (act > 0) {
+      if (ok && act > 0) {
         ok = mbar_wait_warp(bar(L::kDkvEmpty + prev_kind), (empty_par >> prev_kind) & 1u, abort_flag, kSiteBase + 33);
         empty_par ^= 1u << prev_kind;
       }
@@ -871,8 +872,10 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         issue_acc(kColDv, kColS + 128u * (uint32_t)sbuf(gt), do_lo0 + (uint32_t)st * kStageStep, acc0);
         if (!kTwoS) mma_commit(leader, bar(L::kSFree));
         mma_commit(leader, bar(L::kDoEmpty + st));
-        // dK += dS^T Q
-        ok = mbar_wait_warp(bar(L::kDsReady), par, abort_flag, kSiteBase + 9);
+        // dK += dS^T Q  (dS exists only if Q_i had landed for S^T; waited for here all the same, like K_j / V_j
+        // above: every product waits for the arrival of each tile it reads, on this warp's own account)
+        ok = mbar_wait_warp(bar(L::kQFull + st), (uint32_t)(gt >> 1) & 1u, abort_flag, kSiteBase + 23);
+        ok = ok && mbar_wait_warp(bar(L::kDsReady), par, abort_flag, kSiteBase + 9);
         if (!ok) break;
         tc_fence_after_sync();
         if constexpr (kTwoS) {
