@@ -872,10 +872,9 @@ sigattn_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_const
         issue_acc(kColDv, kColS + 128u * (uint32_t)sbuf(gt), do_lo0 + (uint32_t)st * kStageStep, acc0);
         if (!kTwoS) mma_commit(leader, bar(L::kSFree));
         mma_commit(leader, bar(L::kDoEmpty + st));
-        // dK += dS^T Q  (dS exists only if Q_i had landed for S^T; waited for here all the same, like K_j / V_j
-        // above: every product waits for the arrival of each tile it reads, on this warp's own account)
-        ok = mbar_wait_warp(bar(L::kQFull + st), (uint32_t)(gt >> 1) & 1u, abort_flag, kSiteBase + 23);
-        ok = ok && mbar_wait_warp(bar(L::kDsReady), par, abort_flag, kSiteBase + 9);
+        // dK += dS^T Q  (no wait for Q_i of this warp's own: dS exists only because S^T = K Q^T was computed
+        // from the landed tile, so its arrival precedes the barrier below)
+        ok = mbar_wait_warp(bar(L::kDsReady), par, abort_flag, kSiteBase + 9);
         if (!ok) break;
         tc_fence_after_sync();
         if constexpr (kTwoS) {
