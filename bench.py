@@ -370,7 +370,7 @@ EXTRA_WORKLOADS = ["cfg2-causal", "cfg3", "cfg3-causal", "cfg4", "sweep:512:64:b
 # workload (dense fp16, B=4, N=4096, H=16, D=64), from an `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum
 # --clock-control none -k regex:<kernel> -c 1` capture of this very launch; None = not captured for the
 # current kernels.  Only reported for that workload on one GPU.
-NCU_DRAM_BYTES_DEFAULT_WORKLOAD = {"sigattn_bwd_kernel": 202008064 + 92599040, "sigattn_fwd_kernel": 100861440 + 15156992}
+NCU_DRAM_BYTES_DEFAULT_WORKLOAD = {"sigattn_bwd_kernel": 201936384 + 93511424, "sigattn_fwd_kernel": 100867072 + 14927360}
 
 
 class Dist:
