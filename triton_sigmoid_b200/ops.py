@@ -349,7 +349,13 @@ def _varlen_params(q, k, v, cu_q, cu_k, max_q, max_k, bias, score_mod, scale, is
     p.q_strides, p.k_strides, p.v_strides = s3(q), s3(k), s3(v)
     p.cu_seqlens_q, p.cu_seqlens_k = cu_q.data_ptr(), cu_k.data_ptr()
     p.total_q, p.total_k = total_q, k.shape[0]
-    p.bias = bias.data_ptr()
+    if isinstance(bias, torch.Tensor):
+        p.bias = bias.data_ptr()
+    elif bias is None:  # -log(number of keys of the sequence), computed by the kernels
+        p.bias = None
+        p.flags |= _cabi.SIGATTN_BIAS_NEG_LOG_LK
+    else:
+        p.bias, p.bias_scalar = None, float(bias)
     p.score_mod = score_mod.data_ptr() if score_mod is not None else None
     p.stream = torch.cuda.current_stream(q.device).cuda_stream
     return p
@@ -368,6 +374,11 @@ def _check_varlen_kernel_inputs(q, k, v):
 def sigmoid_attn_varlen_fwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, cu_seqlens_q: torch.Tensor,
                                cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, bias: torch.Tensor,
                                score_mod: Optional[torch.Tensor], sm_scale: float, is_causal: bool) -> torch.Tensor:
+    return _run_varlen_fwd(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, bias, score_mod, sm_scale,
+                           is_causal)
+
+
+def _run_varlen_fwd(Q, K, V, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, bias, score_mod, sm_scale, is_causal):
     _check_varlen_kernel_inputs(Q, K, V)
     Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
     # only rows of the sequences are written: rows between or behind them, and rows of a sequence beyond
@@ -396,6 +407,12 @@ def sigmoid_attn_varlen_bwd_op(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor
                                cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_q: int,
                                max_seqlen_k: int, bias: torch.Tensor, score_mod: Optional[torch.Tensor],
                                sm_scale: float, is_causal: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _run_varlen_bwd(Q, K, V, dO, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, bias, score_mod, sm_scale,
+                           is_causal)
+
+
+def _run_varlen_bwd(Q, K, V, dO, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, bias, score_mod, sm_scale,
+                    is_causal):
     _check_varlen_kernel_inputs(Q, K, V)
     Q, K, V, dO = Q.contiguous(), K.contiguous(), V.contiguous(), dO.contiguous()
     # rows between or behind the sequences (there are none when cu_seqlens covers the tensors) stay zero
@@ -441,6 +458,26 @@ def _varlen_backward(ctx, dO):
 
 
 sigmoid_attn_varlen_fwd_op.register_autograd(_varlen_backward, setup_context=_varlen_setup_context)
+
+
+class _EagerSigmoidAttentionVarlen(torch.autograd.Function):
+    """The packed entry point's counterpart of :class:`_EagerSigmoidAttention` (same reasons, same `bias` forms)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, bias, score_mod, scale, is_causal):
+        bias_t = bias if isinstance(bias, torch.Tensor) else None
+        ctx.save_for_backward(q, k, v, cu_q, cu_k, bias_t, score_mod)
+        ctx.bias_value = None if bias_t is not None else bias
+        ctx.max_q, ctx.max_k, ctx.scale, ctx.is_causal = max_q, max_k, scale, is_causal
+        return _run_varlen_fwd(q, k, v, cu_q, cu_k, max_q, max_k, bias, score_mod, scale, is_causal)
+
+    @staticmethod
+    def backward(ctx, dO):
+        q, k, v, cu_q, cu_k, bias_t, score_mod = ctx.saved_tensors
+        bias = bias_t if bias_t is not None else ctx.bias_value
+        dq, dk, dv = _run_varlen_bwd(q, k, v, dO, cu_q, cu_k, ctx.max_q, ctx.max_k, bias, score_mod, ctx.scale,
+                                     ctx.is_causal)
+        return dq, dk, dv, None, None, None, None, None, None, None, None
 
 
 # ----------------------------------------------------------------------------- public API
@@ -656,12 +693,21 @@ def sigmoid_attention_varlen(
     Dk = _kernel_head_dim(D)
     query, key, value = (_pad_head_dim(t, Dk).contiguous() for t in (query, key, value))
 
-    if sigmoid_bias is None:
-        lens_k = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).clamp(min=0, max=int(max_seqlen_k))
-        bias = -torch.log(lens_k.float())  # +inf for an empty key set; every probability is masked there anyway
+    if torch.compiler.is_compiling():
+        if sigmoid_bias is None:
+            lens_k = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).clamp(min=0, max=int(max_seqlen_k))
+            bias = -torch.log(lens_k.float())  # +inf for an empty key set; every probability is masked there anyway
+        else:
+            bias = torch.full((B,), float(sigmoid_bias), dtype=torch.float32, device=query.device)
+        out = sigmoid_attn_varlen_fwd_op(query, key, value, cu_seqlens_q, cu_seqlens_k, int(max_seqlen_q),
+                                         int(max_seqlen_k), bias, score_mod, float(scale), bool(is_causal))
     else:
-        bias = torch.full((B,), float(sigmoid_bias), dtype=torch.float32, device=query.device)
-
-    out = sigmoid_attn_varlen_fwd_op(query, key, value, cu_seqlens_q, cu_seqlens_k, int(max_seqlen_q),
-                                     int(max_seqlen_k), bias, score_mod, float(scale), bool(is_causal))
+        # eager: no dispatcher round trip, the default bias computed by the kernels, an explicit one passed by value
+        bias = None if sigmoid_bias is None else float(sigmoid_bias)
+        args = (query, key, value, cu_seqlens_q, cu_seqlens_k, int(max_seqlen_q), int(max_seqlen_k), bias, score_mod,
+                float(scale), bool(is_causal))
+        if torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad):
+            out = _EagerSigmoidAttentionVarlen.apply(*args)
+        else:
+            out = _run_varlen_fwd(*args)
     return out if Dk == D else out[..., :D]
